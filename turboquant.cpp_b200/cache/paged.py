@@ -10,7 +10,8 @@ its recurrent layers' fixed-size state in the same object, zeroed at creation
   window).  Each group has its own pool of pages and each sequence its own page list per group,
   so layers that keep every key and layers that keep a window of them are stored apart; a
   windowed group gives pages back as they fall out of every later query's sight.
-* an entry's storage is one tensor [pages, 2 (K, V), kv heads, page_size, head size].
+* an entry's storage is one tensor [pages, planes, kv heads, page_size, head size]: two planes (K, V), or one
+  for a mixer whose cached row serves as key and value.
 * a sequence holds a *slot*: its row in every state tensor [max_slots, *shape].  The row is
   zeroed when the slot is taken.  Slots and pages are given back when the sequence is closed and
   are used again by later sequences.
@@ -32,7 +33,8 @@ class PagedCache:
     def __init__(self, kv_needs: Sequence[Optional[KVNeed]], state_needs: Sequence[Optional[StateNeed]],
                  cache_of: Sequence[Optional[int]], max_tokens: int, dtype: torch.dtype, device,
                  max_slots: Optional[int] = None, page_size: int = PAGE_SIZE,
-                 pages_per_group: Optional[Dict[KVNeed, int]] = None):
+                 pages_per_group: Optional[Dict[KVNeed, int]] = None,
+                 embed_state_need: Optional[StateNeed] = None):
         """kv_needs/state_needs/cache_of: one item per entry of the model's layer schedule.
         max_tokens: the most tokens live sequences hold together, each sequence's count rounded up
         to a multiple of page_size."""
@@ -65,7 +67,7 @@ class PagedCache:
                 self.kv.append(None)
                 continue
             g = self.entry_group[i]
-            self.kv.append(torch.zeros((counts[g], 2, need.n_kv_heads, self.page_size, need.head_dim),
+            self.kv.append(torch.zeros((counts[g], need.planes, need.n_kv_heads, self.page_size, need.head_dim),
                                        dtype=dtype, device=self.device))
         for i, src in enumerate(cache_of):
             if src is not None:
@@ -74,11 +76,14 @@ class PagedCache:
         self.state: List[Optional[torch.Tensor]] = [
             None if n is None else torch.zeros((self.max_slots,) + tuple(n.shape), dtype=n.dtype, device=self.device)
             for n in state_needs]
+        # state the embedding keeps per sequence (a design whose embedding looks at the token before)
+        self.embed_state: Optional[torch.Tensor] = None if embed_state_need is None else torch.zeros(
+            (self.max_slots,) + tuple(embed_state_need.shape), dtype=embed_state_need.dtype, device=self.device)
 
     # ---- sequences ------------------------------------------------------------------------------
     def open(self) -> Sequence_:
         seq = self.book.open()
-        for s in self.state:
+        for s in self.state + [self.embed_state]:
             if s is not None:
                 s[seq.slot].zero_()
         return seq
@@ -119,5 +124,5 @@ class PagedCache:
     def bytes_per_token(self) -> int:
         """Key/value bytes one token adds across all layers that keep a cache."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * t.shape[2] * t.shape[4] * el for i, t in enumerate(self.kv)
+        return sum(t.shape[1] * t.shape[2] * t.shape[4] * el for i, t in enumerate(self.kv)
                    if t is not None and self.cache_of[i] is None)

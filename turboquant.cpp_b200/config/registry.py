@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration and model.
 
-config.json names the architecture in ``architectures[0]``; the registry maps
+config.json names the architecture in ``architectures[0]`` (or in one string, ``architecture``); the registry maps
 that name to the class that reads the rest of the file and to the class that
 builds the model from it.  The reference selects model code by an integer
 ``model_type`` and substring tests on the GGUF architecture string
@@ -47,8 +47,11 @@ def registered_architectures() -> Tuple[str, ...]:
 
 def architecture_name(raw: Dict[str, Any], where: str = "config.json") -> str:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):      # some designs name themselves with one string
+        return raw["architecture"]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names "
+                          f"(or 'architecture' one name)")
     return archs[0]
 
 

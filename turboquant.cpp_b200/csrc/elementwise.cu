@@ -325,3 +325,170 @@ TQ_EXPORT int tq_gather_rows(const void* in, const int* idx, int divisor, void* 
     TQ_CHECK_LAUNCH("gather_rows");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Embedding with a scale and a table of token pairs:
+//   x[t] = table[tok] * scale + pair[(prev * mul_prev + tok * mul_cur) mod buckets]
+// where prev is the token before tok in its sequence; a sequence's first token takes the pair table's row
+// `buckets`.  The token before a step's first token comes from last_token[slot], the sequence's state; the block
+// of a sequence's first token of the step reads it and then stores the step's last token there (one thread, read
+// before write, and no other block touches that slot).  pair == nullptr: no pair table, no state.
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_pair_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                       const TW* __restrict__ pair, float* __restrict__ x, int H, int V, float scale,
+                                       int buckets, long long mul_prev, long long mul_cur,
+                                       const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
+                                       const int* __restrict__ seq_start, const int* __restrict__ slots,
+                                       int* __restrict__ last_token, int n_seqs) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ int s_row;
+    const int t = blockIdx.x;
+    const int tok = TQ_CHECKED(tokens[t], V, TQ_IDX_TOKEN);
+    if (pair && threadIdx.x == 0) {
+        const int s = TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE);
+        const int first = cu_seqlens[s];
+        long long prev = -1;
+        if (t > first) {
+            prev = tokens[t - 1];
+        } else {
+            if (seq_start[s] > 0) prev = last_token[slots[s]];
+            last_token[slots[s]] = tokens[cu_seqlens[s + 1] - 1];
+        }
+        long long r = buckets;
+        if (prev >= 0) {
+            r = (prev * mul_prev + (long long)tok * mul_cur) % buckets;
+            if (r < 0) r += buckets;
+        }
+        s_row = (int)r;
+    }
+    __syncthreads();
+    const TW* row = table + (size_t)tok * H;
+    const TW* prow = pair ? pair + (size_t)s_row * H : nullptr;
+    float* out = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = tq_to_float(row[i]) * scale;
+        if (prow) v += tq_to_float(prow[i]);
+        out[i] = v;
+    }
+}
+
+TQ_EXPORT int tq_embed_pair_rows(const int* tokens, const void* table, const void* pair, int table_dtype, float* x,
+                                 int T_, int H, int V, float scale, int buckets, long long mul_prev, long long mul_cur,
+                                 const int* seq_of_token, const int* cu_seqlens, const int* seq_start, const int* slots,
+                                 int* last_token, int n_seqs, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && H > 0, "embed_pair_rows: bad sizes T=%d H=%d", T_, H);
+    TQ_REQUIRE(!pair || (buckets > 0 && last_token), "embed_pair_rows: a pair table needs buckets and a state");
+    const int threads = H >= 1024 ? 256 : 128;
+    TQ_DISPATCH(table_dtype, TW,
+        tq_launch(T_, threads, 0, stream)(embed_pair_rows_kernel<TW>, tokens, (const TW*)table, (const TW*)pair, x, H, V,
+                                          scale, buckets, mul_prev, mul_cur, seq_of_token, cu_seqlens, seq_start, slots,
+                                          last_token, n_seqs));
+    TQ_CHECK_LAUNCH("embed_pair_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Residual sum with the norm on the sub-layer's output: x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w, in fp32;
+// `copy` (optional) receives the new x in the activation dtype for the products that read it next.
+// ---------------------------------------------------------------------------------------
+template <typename TY, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__ y, const TW* __restrict__ w,
+                                   TO* __restrict__ copy, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const TY* yr = y + r * H;
+    float* xr = x + r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = tq_to_float(yr[i]);
+        ss += v * v;
+    }
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i] + tq_to_float(yr[i]) * rs * tq_to_float(w[i]);
+        xr[i] = v;
+        if (copy) copy[r * H + i] = tq_from_float<TO>(v);
+    }
+}
+
+TQ_EXPORT int tq_add_rmsnorm(float* x, const void* y, int y_dtype, const void* w, int w_dtype, void* copy,
+                             int copy_dtype, int R, int H, float eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    TQ_REQUIRE(R > 0 && H > 0, "add_rmsnorm: bad sizes R=%d H=%d", R, H);
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,
+        (tq_launch(R, threads, 0, stream)(add_rmsnorm_kernel<TY, TW, TO>, x, (const TY*)y, (const TW*)w, (TO*)copy, H,
+                                          eps)))));
+    TQ_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[i] = act(in[i]) elementwise; act 0: identity (a change of dtype), 1: the square of relu
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void map_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n, int act) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        float v = tq_to_float(in[i]);
+        if (act == 1) { v = fmaxf(v, 0.f); v = v * v; }
+        out[i] = tq_from_float<TO>(v);
+    }
+}
+
+TQ_EXPORT int tq_map(const void* in, int in_dtype, void* out, int out_dtype, long long n, int act, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TQ_REQUIRE(act == 0 || act == 1, "map: unknown function %d", act);
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch((int)blocks, threads, 0, stream)(map_kernel<TI, TO>, (const TI*)in, (TO*)out, (size_t)n, act))));
+    TQ_CHECK_LAUNCH("map");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Rotation of interleaved pairs in place: rows [T, heads, row] (row stride given), the pairs (2i, 2i+1) of the
+// `n_pairs` first pairs from element `offset` of each head turn by angle = position * freq[i]; cos and sin carry the
+// factor `mag`.  Angles in fp32.
+// ---------------------------------------------------------------------------------------
+template <typename TX>
+__global__ void rotate_pairs_kernel(TX* __restrict__ x, const float* __restrict__ freq, const int* __restrict__ positions,
+                                    int heads, int head_stride, long long token_stride, int offset, int n_pairs, float mag) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int k = threadIdx.x; k < heads * n_pairs; k += blockDim.x) {
+        const int h = k / n_pairs, i = k % n_pairs;
+        float s, c;
+        sincosf(pos * freq[i], &s, &c);
+        s *= mag; c *= mag;
+        TX* p = x + (size_t)t * token_stride + (size_t)h * head_stride + offset + 2 * i;
+        const float u = tq_to_float(p[0]), v = tq_to_float(p[1]);
+        p[0] = tq_from_float<TX>(u * c - v * s);
+        p[1] = tq_from_float<TX>(v * c + u * s);
+    }
+}
+
+TQ_EXPORT int tq_rotate_pairs(void* x, int dtype, const float* freq, const int* positions, int T_, int heads,
+                              int head_stride, long long token_stride, int offset, int n_pairs, float mag,
+                              cudaStream_t stream) {
+    if (T_ == 0 || n_pairs == 0 || heads == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && heads > 0 && n_pairs > 0 && offset >= 0, "rotate_pairs: bad sizes");
+    TQ_DISPATCH(dtype, TX,
+        tq_launch(T_, 128, 0, stream)(rotate_pairs_kernel<TX>, (TX*)x, freq, positions, heads, head_stride, token_stride,
+                                      offset, n_pairs, mag));
+    TQ_CHECK_LAUNCH("rotate_pairs");
+    return 0;
+}

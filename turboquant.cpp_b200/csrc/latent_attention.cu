@@ -1,0 +1,311 @@
+// Attention over a cache of latent rows.
+//
+// A layer of this kind caches ONE row per position, shared by all heads: [c | kr], the latent c (R elements, already
+// normed) and a rotated key part kr (rot elements).  Head a's key is W_uk,a c and its value W_uv,a c, so with
+//   q~_a = W_uk,a^T q_a            (the query carried into the latent space, R elements)
+// the score is (q~_a . c + q_a,rot . kr) * scale and the head's output is W_uv,a applied to sum_j p_j c_j: attention
+// with one key/value head whose value is the first R elements of its key row.  The two products with W_uk and W_uv
+// are batched matrix products outside; the kernels here are
+//   latent_prepare    norm of the latent, rotation of kr and of the queries' rotated part, cache write
+//   latent_attention  scores, softmax with an optional sink per head, weighted sum of latents
+//   latent_merge      joins the key ranges of a split launch
+// Scores, softmax and sums are fp32.  A sink is a learned logit per head that takes part in the softmax's
+// denominator and has no value: out = sum_j e^{s_j - M} c_j / (sum_j e^{s_j - M} + e^{sink - M}).
+// Window w > 0: position i sees j with 0 <= i - j < w.
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+#define LAT_MAX_ROW 1024      // R + rot at most
+#define LAT_WARPS 4
+#define LAT_HG 4              // heads per block: they share every key row the block loads
+
+// ---------------------------------------------------------------------------------------
+// latent_prepare: one block per token.
+//   dkv given: row = [ d[0:R] / sqrt(mean(d[0:R]^2) + eps) * wnorm | rotate(d[R:R+rot]) ] -> cache at the token's place
+//   q: the rotated part of every head (elements q_off .. q_off+rot of a head of q_dim elements) turns in place
+// Rotation: pairs (2i, 2i+1), i < n_pairs, angle = position * freq[i] in fp32, cos and sin times mag; elements
+// beyond 2 n_pairs pass unchanged.
+// ---------------------------------------------------------------------------------------
+template <typename TA, typename TW>
+__global__ void latent_prepare_kernel(TA* __restrict__ q, const float* __restrict__ dkv, const TW* __restrict__ wnorm,
+                                      float eps, const float* __restrict__ freq, float mag,
+                                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                      const int* __restrict__ page_table, int table_stride, int page_size,
+                                      TA* __restrict__ cache, int heads, int q_dim, int q_off, int rot, int n_pairs,
+                                      int R, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const float fpos = (float)pos;
+    if (dkv) {
+        const float* d = dkv + (size_t)t * (R + rot);
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < R; i += blockDim.x) ss += d[i] * d[i];
+        ss = tq_block_sum(ss, scratch);
+        const float rs = 1.0f / sqrtf(ss / (float)R + eps);
+        const int seq = TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE);
+        const int page = TQ_CHECKED(page_table[(size_t)seq * table_stride + TQ_CHECKED(pos / page_size, table_stride, TQ_IDX_TABLE_COLUMN)],
+                                    n_pages, TQ_IDX_PAGE);
+        TA* row = cache + ((size_t)page * page_size + pos % page_size) * (R + rot);
+        for (int i = threadIdx.x; i < R; i += blockDim.x) row[i] = tq_from_float<TA>(d[i] * rs * tq_to_float(wnorm[i]));
+        for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+            float s, c;
+            sincosf(fpos * freq[i], &s, &c);
+            s *= mag; c *= mag;
+            const float u = d[R + 2 * i], v = d[R + 2 * i + 1];
+            row[R + 2 * i] = tq_from_float<TA>(u * c - v * s);
+            row[R + 2 * i + 1] = tq_from_float<TA>(v * c + u * s);
+        }
+        for (int e = 2 * n_pairs + threadIdx.x; e < rot; e += blockDim.x) row[R + e] = tq_from_float<TA>(d[R + e]);
+    }
+    for (int k = threadIdx.x; k < heads * n_pairs; k += blockDim.x) {
+        const int h = k / n_pairs, i = k % n_pairs;
+        float s, c;
+        sincosf(fpos * freq[i], &s, &c);
+        s *= mag; c *= mag;
+        TA* p = q + ((size_t)t * heads + h) * q_dim + q_off + 2 * i;
+        const float u = tq_to_float(p[0]), v = tq_to_float(p[1]);
+        p[0] = tq_from_float<TA>(u * c - v * s);
+        p[1] = tq_from_float<TA>(v * c + u * s);
+    }
+}
+
+TQ_EXPORT int tq_latent_prepare(void* q, int act_dtype, const float* dkv, const void* wnorm, int w_dtype, float eps,
+                                const float* freq, float mag, const int* positions, const int* seq_of_token,
+                                const int* page_table, int table_stride, int page_size, void* cache, int T_, int heads,
+                                int q_dim, int q_off, int rot, int n_pairs, int R, int n_seqs, int n_pages,
+                                cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && R >= 1 && rot >= 0 && R + rot <= LAT_MAX_ROW, "latent_prepare: bad sizes R=%d rot=%d", R, rot);
+    TQ_REQUIRE(2 * n_pairs <= rot && q_off >= 0 && q_off + rot <= q_dim, "latent_prepare: the rotated part does not fit "
+               "(pairs %d, rot %d, offset %d, head %d)", n_pairs, rot, q_off, q_dim);
+    TQ_REQUIRE(!dkv || (cache && page_table && wnorm), "latent_prepare: a projection to cache needs a cache and a norm");
+    TQ_REQUIRE(n_pairs == 0 || freq, "latent_prepare: a rotation needs frequencies");
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
+        (tq_launch(T_, 128, 0, stream)(latent_prepare_kernel<TA, TW>, (TA*)q, dkv, (const TW*)wnorm, eps, freq, mag,
+                                       positions, seq_of_token, page_table, table_stride, page_size, (TA*)cache, heads,
+                                       q_dim, q_off, rot, n_pairs, R, n_seqs, n_pages))));
+    TQ_CHECK_LAUNCH("latent_prepare");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// latent_attention: grid (tokens, ceil(heads / LAT_HG), n_splits), LAT_WARPS warps.  The block's keys (its share of
+// the token's range) go round the warps; a lane holds EPL elements of the row in groups of VEC neighbours
+// (element VEC*lane + 32*VEC*j + c), so a warp reads a row with 8- or 16-byte loads; the LAT_HG heads' queries
+// lie in shared memory.  Each warp keeps an online softmax per head; the warps' states are joined through shared
+// memory in warp order.  n_splits == 1: the sink joins and the result is written; otherwise the block's state
+// (max, sum, R weighted elements) goes to `partial` and latent_merge finishes.
+// ---------------------------------------------------------------------------------------
+template <typename TA, int VEC> struct LatRow;
+template <> struct LatRow<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float* o) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+};
+template <> struct LatRow<__nv_bfloat16, 4> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+        o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+    }
+};
+template <typename TA> struct LatRow<TA, 1> {
+    static __device__ __forceinline__ void load(const TA* p, float* o) { o[0] = tq_to_float(*p); }
+};
+
+template <typename TA, int EPL, int VEC>
+__global__ void __launch_bounds__(LAT_WARPS * 32)
+latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, int q_dim, int q_off,
+                        const TA* __restrict__ cache, const float* __restrict__ sink,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ page_table, int table_stride, int page_size, int window, float scale,
+                        TA* __restrict__ out, float* __restrict__ partial, int H, int R, int rot, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ float lat_smem[];
+    __shared__ float s_m[LAT_WARPS][LAT_HG], s_l[LAT_WARPS][LAT_HG];
+    constexpr int NG = EPL / VEC;
+    const int Dk = R + rot;
+    float* qs = lat_smem;                       // [LAT_HG][Dk]
+    float* s_acc = lat_smem + LAT_HG * Dk;      // [LAT_WARPS][R]
+    const int t = blockIdx.x, h0 = blockIdx.y * LAT_HG;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < LAT_HG * Dk; k += blockDim.x) {
+        const int g = k / Dk, e = k % Dk, h = h0 + g;
+        float v = 0.f;
+        if (h < H) v = e < R ? tq_to_float(q_lat[((size_t)t * H + h) * R + e])
+                             : tq_to_float(q[((size_t)t * H + h) * q_dim + q_off + (e - R)]);
+        qs[k] = v;
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int n_keys = pos + 1 - first;
+    const int per = (n_keys + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int lo = first + (int)blockIdx.z * per, hi = min(pos + 1, lo + per);
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+
+    float m[LAT_HG], l[LAT_HG], acc[LAT_HG][EPL];
+#pragma unroll
+    for (int g = 0; g < LAT_HG; ++g) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) acc[g][j] = 0.f;
+    }
+    for (int p = lo + warp; p < hi; p += LAT_WARPS) {
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+        const TA* kp = cache + ((size_t)page * page_size + p % page_size) * Dk;
+        float kr[EPL];
+#pragma unroll
+        for (int j = 0; j < NG; ++j) {
+            const int e = VEC * lane + 32 * VEC * j;
+            if (e < Dk) LatRow<TA, VEC>::load(kp + e, kr + VEC * j);
+            else {
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) kr[VEC * j + c] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < LAT_HG; ++g) {
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < NG; ++j) {
+                const int e = VEC * lane + 32 * VEC * j;
+                if (e < Dk) {
+#pragma unroll
+                    for (int c = 0; c < VEC; ++c) s += qs[g * Dk + e + c] * kr[VEC * j + c];
+                }
+            }
+            s = tq_warp_sum(s) * scale;
+            const float m_new = fmaxf(m[g], s);
+            const float corr = expf(m[g] - m_new);          // exp(-inf) = 0 on the first key
+            const float pe = expf(s - m_new);
+            l[g] = l[g] * corr + pe;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) acc[g][j] = acc[g][j] * corr + pe * kr[j];
+            m[g] = m_new;
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < LAT_HG; ++g) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    }
+#pragma unroll
+    for (int g = 0; g < LAT_HG; ++g) {
+        __syncthreads();                 // the round before has been read
+#pragma unroll
+        for (int j = 0; j < NG; ++j) {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                const int e = VEC * lane + 32 * VEC * j + c;
+                if (e < R) s_acc[warp * R + e] = acc[g][VEC * j + c];
+            }
+        }
+        __syncthreads();
+        const int h = h0 + g;
+        if (h >= H) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < LAT_WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+        const bool whole = gridDim.z == 1;
+        const float sk = (whole && sink) ? sink[h] : -INFINITY;
+        M = fmaxf(M, sk);
+        float f[LAT_WARPS], L = 0.f;
+#pragma unroll
+        for (int w = 0; w < LAT_WARPS; ++w) {
+            f[w] = s_m[w][g] == -INFINITY ? 0.f : expf(s_m[w][g] - M);
+            L += s_l[w][g] * f[w];
+        }
+        if (whole) {
+            if (sink) L += expf(sk - M);
+            TA* op = out + ((size_t)t * H + h) * R;
+            for (int e = threadIdx.x; e < R; e += blockDim.x) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < LAT_WARPS; ++w) v += s_acc[w * R + e] * f[w];
+                op[e] = tq_from_float<TA>(v / L);
+            }
+        } else {
+            float* pp = partial + (((size_t)t * H + h) * gridDim.z + blockIdx.z) * (R + 2);
+            if (threadIdx.x == 0) { pp[0] = M; pp[1] = L; }      // an empty range leaves M = -inf, L = 0
+            for (int e = threadIdx.x; e < R; e += blockDim.x) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < LAT_WARPS; ++w) v += s_acc[w * R + e] * f[w];
+                pp[2 + e] = v;
+            }
+        }
+    }
+}
+
+// joins the ranges of one (token, head) in range order and lets the sink take part
+template <typename TA>
+__global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, int n_splits,
+                                    int H, int R, TA* __restrict__ out) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* pp = partial + ((size_t)t * H + h) * n_splits * (R + 2);
+    const float sk = sink ? sink[h] : -INFINITY;
+    float M = sk;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, pp[(size_t)s * (R + 2)]);
+    float L = sink ? expf(sk - M) : 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = pp[(size_t)s * (R + 2)];
+        if (ms != -INFINITY) L += pp[(size_t)s * (R + 2) + 1] * expf(ms - M);
+    }
+    for (int e = threadIdx.x; e < R; e += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = pp[(size_t)s * (R + 2)];
+            if (ms != -INFINITY) v += pp[(size_t)s * (R + 2) + 2 + e] * expf(ms - M);
+        }
+        out[((size_t)t * H + h) * R + e] = tq_from_float<TA>(v / L);
+    }
+}
+
+#define LAT_LAUNCH(TA, EPL, VEC)                                                                                  \
+    tq_launch(grid, LAT_WARPS * 32, smem, stream)(latent_attention_kernel<TA, EPL, VEC>, (const TA*)q_lat,        \
+        (const TA*)q, q_dim, q_off, (const TA*)cache, sink, positions, seq_of_token, page_table, table_stride,    \
+        page_size, window, scale, (TA*)out, partial, H, R, rot, n_seqs, n_pages)
+
+TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, int q_off, const void* cache,
+                                  int act_dtype, const float* sink, const int* positions, const int* seq_of_token,
+                                  const int* page_table, int table_stride, int page_size, int window, float scale,
+                                  void* out, float* partial, int n_splits, int T_, int H, int R, int rot, int n_seqs,
+                                  int n_pages, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    const int Dk = R + rot;
+    TQ_REQUIRE(H >= 1 && R >= 1 && rot >= 0 && Dk <= LAT_MAX_ROW, "latent_attention: a row of %d + %d elements exceeds %d",
+               R, rot, LAT_MAX_ROW);
+    TQ_REQUIRE(window >= 0, "latent_attention: negative window %d", window);
+    TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || partial), "latent_attention: %d key ranges need a "
+               "scratch buffer", n_splits);
+    TQ_REQUIRE((H + LAT_HG - 1) / LAT_HG <= 65535, "latent_attention: %d heads exceed the grid limit", H);
+    TQ_REQUIRE(rot == 0 || (q && q_off >= 0 && q_off + rot <= q_dim), "latent_attention: the queries' rotated part does not fit");
+    dim3 grid(T_, (H + LAT_HG - 1) / LAT_HG, n_splits);
+    const size_t smem = (size_t)(LAT_HG * Dk + LAT_WARPS * R) * sizeof(float);
+    const bool vec = Dk % 4 == 0 && R % 4 == 0 && ((uintptr_t)cache % 16) == 0;
+    TQ_DISPATCH(act_dtype, TA, {
+        if (!vec) LAT_LAUNCH(TA, 32, 1);
+        else if (Dk <= 128) LAT_LAUNCH(TA, 4, 4);
+        else if (Dk <= 256) LAT_LAUNCH(TA, 8, 4);
+        else if (Dk <= 640) LAT_LAUNCH(TA, 20, 4);
+        else LAT_LAUNCH(TA, 32, 4);
+    });
+    TQ_CHECK_LAUNCH("latent_attention");
+    if (n_splits > 1) {
+        dim3 mgrid(T_, H);
+        TQ_REQUIRE(H <= 65535, "latent_attention: %d heads exceed the grid limit", H);
+        TQ_DISPATCH(act_dtype, TA,
+            (tq_launch(mgrid, 128, 0, stream)(latent_merge_kernel<TA>, (const float*)partial, sink, n_splits, H, R, (TA*)out)));
+        TQ_CHECK_LAUNCH("latent_merge");
+    }
+    return 0;
+}

@@ -1,0 +1,235 @@
+// A state-space mixer with a scalar decay per head (the recurrence of Mamba-2) and the short causal convolution
+// in front of it.  Per head a with state S [N, vdim] (fp32, one per sequence, carried from step to step):
+//   dt   = softplus(dt_raw + dt_bias_a)
+//   S   <- exp(-exp(A_log_a) * dt) * S + dt * B x^T
+//   y    = S^T C + D_a x
+// B and C [N] belong to the head's group (head a uses group a / (heads / groups)).  x, B and C are the output of
+// a causal convolution per channel over the projection's xBC part (`taps` taps, the last on the current token,
+// zeros before a sequence's start) followed by silu; the last taps-1 inputs of a sequence are part of its state.
+// Everything here is fp32: the projection arrives as fp32, decays, step sizes and the state never leave it.
+//   conv_silu          the convolution over the step's tokens, reading the kept inputs for a run's first tokens
+//   conv_state_update  the kept inputs after the step (a launch of its own: conv_silu reads the old ones)
+//   ssm_scan           the recurrence over each sequence's run of new tokens, state in registers
+//   gated_group_norm   y * silu(z), RMS norm in equal groups, weight
+#include "common.cuh"
+
+TQ_DEFINE_LAST_ERROR
+
+#define SSM_MAX_TAPS 8
+#define SSM_MAX_STATE 256
+#define SSM_NPT 32            // rows of the state a thread keeps
+#define SSM_VT 32             // columns of the state per block (a warp's lanes)
+
+template <typename TW>
+__global__ void conv_silu_kernel(const float* __restrict__ proj, int P, int off, const TW* __restrict__ w,
+                                 const TW* __restrict__ b, const float* __restrict__ kept, long long slot_stride,
+                                 float* __restrict__ out, int C, int taps, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int n_seqs) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int s = TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE);
+    const int i = t - cu_seqlens[s];                 // place in the sequence's run of new tokens
+    const float* old = kept + (size_t)slots[s] * slot_stride;      // [taps-1][C]: inputs of the positions just before the run
+    float acc = b ? tq_to_float(b[c]) : 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k, src = i - back;
+        const float v = src >= 0 ? proj[(size_t)(t - back) * P + off + c] : old[(size_t)(taps - 1 + src) * C + c];
+        acc += tq_to_float(w[(size_t)c * taps + k]) * v;
+    }
+    out[(size_t)t * C + c] = acc / (1.0f + expf(-acc));
+}
+
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, int P, int off, float* __restrict__ kept,
+                                         long long slot_stride, int C, int taps, const int* __restrict__ cu_seqlens,
+                                         const int* __restrict__ slots) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = cu_seqlens[s], n = cu_seqlens[s + 1] - first;
+    float* old = kept + (size_t)slots[s] * slot_stride;
+    float v[SSM_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < SSM_MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+            const int idx = j + n - (taps - 1);          // place in the run of the input that is kept at j from now on
+            v[j] = idx >= 0 ? proj[(size_t)(first + idx) * P + off + c] : old[(size_t)(j + n) * C + c];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < SSM_MAX_TAPS - 1; ++j)
+        if (j < taps - 1) old[(size_t)j * C + c] = v[j];
+}
+
+TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, const void* b, int w_dtype, float* kept,
+                           long long slot_stride, float* out, int T_, int C, int taps, const int* seq_of_token,
+                           const int* cu_seqlens, const int* slots, int n_seqs, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(C >= 1 && taps >= 1 && taps <= SSM_MAX_TAPS, "conv_silu: %d taps (1..%d)", taps, SSM_MAX_TAPS);
+    TQ_REQUIRE(off >= 0 && off + C <= P, "conv_silu: channels %d..%d outside the projection's %d", off, off + C, P);
+    const int threads = 128;
+    dim3 grid(T_, (C + threads - 1) / threads);
+    TQ_REQUIRE(grid.y <= 65535, "conv_silu: %d channels exceed the grid limit", C);
+    TQ_DISPATCH(w_dtype, TW,
+        (tq_launch(grid, threads, 0, stream)(conv_silu_kernel<TW>, proj, P, off, (const TW*)w, (const TW*)b,
+                                             (const float*)kept, slot_stride, out, C, taps, seq_of_token, cu_seqlens, slots, n_seqs)));
+    TQ_CHECK_LAUNCH("conv_silu");
+    if (taps > 1) {
+        dim3 ugrid(n_seqs, (C + threads - 1) / threads);
+        tq_launch(ugrid, threads, 0, stream)(conv_state_update_kernel, proj, P, off, kept, slot_stride, C, taps, cu_seqlens, slots);
+        TQ_CHECK_LAUNCH("conv_state_update");
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_VT)), block (SSM_VT, NS): thread (v, part) keeps rows
+// part*SSM_NPT .. of column v of the state in registers for the whole run.  The run is walked in chunks of TC
+// steps: the chunk's B, C, x, step sizes and decays are staged in shared memory, every thread advances its rows
+// through the chunk and leaves its share of each step's y, and the shares are added in part order.
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
+                                const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
+                                float* __restrict__ state, long long slot_stride, float* __restrict__ y,
+                                int heads, int vdim, int N, int groups, int TC, const int* __restrict__ cu_seqlens,
+                                const int* __restrict__ slots) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ float ssm_smem[];
+    const int NS = blockDim.y;
+    float* Bs = ssm_smem;                    // [TC][N]
+    float* Cs = Bs + TC * N;                 // [TC][N]
+    float* xs = Cs + TC * N;                 // [TC][SSM_VT]
+    float* yp = xs + TC * SSM_VT;            // [TC][NS][SSM_VT]
+    float* dts = yp + TC * NS * SSM_VT;      // [TC]
+    float* dec = dts + TC;                   // [TC]
+    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * SSM_VT;
+    const int lane = threadIdx.x, part = threadIdx.y, tid = part * SSM_VT + lane, nthreads = NS * SSM_VT;
+    const int v = v0 + lane;
+    const int g = h / (heads / groups);
+    const int inner = heads * vdim;
+    const int first = cu_seqlens[s], n = cu_seqlens[s + 1] - first;
+    const float A = -expf(tq_to_float(a_log[h])), bias = tq_to_float(dt_bias[h]), D = tq_to_float(d_skip[h]);
+    float* Sg = state + (size_t)slots[s] * slot_stride + ((size_t)h * N) * vdim;
+    float S[SSM_NPT];
+#pragma unroll
+    for (int r = 0; r < SSM_NPT; ++r) {
+        const int row = part * SSM_NPT + r;
+        S[r] = (row < N && v < vdim) ? Sg[(size_t)row * vdim + v] : 0.f;
+    }
+    for (int t0 = 0; t0 < n; t0 += TC) {
+        const int tc = min(TC, n - t0);
+        for (int k = tid; k < tc * N; k += nthreads) {
+            const int tt = k / N, r = k % N;
+            const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + (size_t)g * N + r;
+            Bs[tt * N + r] = row[0];
+            Cs[tt * N + r] = row[(size_t)groups * N];
+        }
+        for (int k = tid; k < tc * SSM_VT; k += nthreads) {
+            const int tt = k / SSM_VT, vv = v0 + k % SSM_VT;
+            xs[k] = vv < vdim ? xbc[(size_t)(first + t0 + tt) * C + (size_t)h * vdim + vv] : 0.f;
+        }
+        if (tid < tc) {
+            const float raw = proj[(size_t)(first + t0 + tid) * P + dt_off + h] + bias;
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            dts[tid] = dt;
+            dec[tid] = expf(A * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < tc; ++tt) {
+            const float a = dec[tt], dtx = dts[tt] * xs[tt * SSM_VT + lane];
+            const float* Bt = Bs + tt * N + part * SSM_NPT;
+            const float* Ct = Cs + tt * N + part * SSM_NPT;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < SSM_NPT; ++r) {
+                if (part * SSM_NPT + r < N) {
+                    S[r] = a * S[r] + dtx * Bt[r];
+                    acc += S[r] * Ct[r];
+                }
+            }
+            yp[(tt * NS + part) * SSM_VT + lane] = acc;
+        }
+        __syncthreads();
+        for (int tt = part; tt < tc; tt += NS) {
+            float acc = 0.f;
+            for (int p = 0; p < NS; ++p) acc += yp[(tt * NS + p) * SSM_VT + lane];
+            if (v < vdim) y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + v] = acc + D * xs[tt * SSM_VT + lane];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < SSM_NPT; ++r) {
+        const int row = part * SSM_NPT + r;
+        if (row < N && v < vdim) Sg[(size_t)row * vdim + v] = S[r];
+    }
+}
+
+TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
+                          const void* a_log, const void* d_skip, int w_dtype, float* state, long long slot_stride,
+                          float* y, int n_seqs, int heads, int vdim, int N, int groups, const int* cu_seqlens,
+                          const int* slots, cudaStream_t stream) {
+    if (n_seqs == 0) return 0;
+    TQ_REQUIRE(heads >= 1 && vdim >= 1 && groups >= 1 && heads % groups == 0, "ssm_scan: %d heads in %d groups", heads, groups);
+    TQ_REQUIRE(N >= 1 && N <= SSM_MAX_STATE, "ssm_scan: state size %d (1..%d)", N, SSM_MAX_STATE);
+    TQ_REQUIRE(C == heads * vdim + 2 * groups * N, "ssm_scan: %d channels for %d heads x %d and %d groups x %d", C, heads, vdim, groups, N);
+    TQ_REQUIRE(dt_off >= 0 && dt_off + heads <= P, "ssm_scan: the step sizes lie outside the projection");
+    const int NS = (N + SSM_NPT - 1) / SSM_NPT;
+    const int TC = N > 128 ? 8 : 16;
+    dim3 grid(n_seqs, heads, (vdim + SSM_VT - 1) / SSM_VT), block(SSM_VT, NS);
+    TQ_REQUIRE(heads <= 65535 && grid.z <= 65535, "ssm_scan: sizes exceed the grid limit");
+    const size_t smem = (size_t)(2 * TC * N + TC * SSM_VT + TC * NS * SSM_VT + 2 * TC) * sizeof(float);
+    TQ_DISPATCH(w_dtype, TW,
+        (tq_launch(grid, block, smem, stream)(ssm_scan_kernel<TW>, xbc, C, proj, P, dt_off, (const TW*)dt_bias,
+                                              (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N,
+                                              groups, TC, cu_seqlens, slots)));
+    TQ_CHECK_LAUNCH("ssm_scan");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, g-th part] = rms(y[t, part] * silu(z[t, part])) * w[part]: the gate first, then the norm of each of the
+// `norm_groups` equal parts by its own root mean square.  z is the first `inner` elements of the projection's row.
+// ---------------------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
+                                        const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t t = blockIdx.x;
+    const int base = blockIdx.y * gs;
+    const float* yr = y + t * inner + base;
+    const float* zr = proj + t * P + z_off + base;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
+        ss += v * v;
+    }
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
+        out[t * inner + base + i] = tq_from_float<TO>(v * rs * tq_to_float(w[base + i]));
+    }
+}
+
+TQ_EXPORT int tq_gated_group_norm(const float* y, const float* proj, int P, int z_off, const void* w, int w_dtype,
+                                  void* out, int out_dtype, int T_, int inner, int norm_groups, float eps,
+                                  cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(inner >= 1 && norm_groups >= 1 && inner % norm_groups == 0 && norm_groups <= 65535,
+               "gated_group_norm: %d elements in %d groups", inner, norm_groups);
+    TQ_REQUIRE(z_off >= 0 && z_off + inner <= P, "gated_group_norm: the gate lies outside the projection");
+    const int gs = inner / norm_groups;
+    dim3 grid(T_, norm_groups);
+    const int threads = gs >= 1024 ? 256 : 128;
+    TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch(grid, threads, 0, stream)(gated_group_norm_kernel<TW, TO>, y, proj, P, z_off, (const TW*)w, (TO*)out,
+                                             inner, gs, eps))));
+    TQ_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+}

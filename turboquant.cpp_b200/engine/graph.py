@@ -40,7 +40,8 @@ class DecodeGraph:
             n_tokens=B, n_seqs=B, tokens=engine.sample_into(B), positions=parts[1], seq_of_token=parts[2], cu_seqlens=parts[3],
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=B, max_q_len=1,
             max_kv_len=engine.table_width * cache.page_size, act_dtype=engine.act_dtype, device=engine.device,
-            host_q_lens=[1] * B, host_slots=[], debug={} if engine.record_routing else None, status=engine.status)
+            host_q_lens=[1] * B, host_slots=[], debug={} if engine.record_routing else None, status=engine.status,
+            embed_state=cache.embed_state)
         for host in self.hosts:              # constant parts of the buffer
             h = host.numpy()
             h[:] = 0

@@ -113,7 +113,8 @@ class Engine:
         self.act_dtype = model.dtype
         ensure_built(model.kernels())
         self.cache = PagedCache(model.cache_needs(), model.state_needs(), [e.cache_of for e in model.schedule],
-                                max_tokens, self.act_dtype, self.device, max_slots=max_slots)
+                                max_tokens, self.act_dtype, self.device, max_slots=max_slots,
+                                embed_state_need=model.embedding_state_need() if hasattr(model, "embedding_state_need") else None)
         self.debug: Optional[Dict[str, Any]] = None
         self.record_routing = bool(record_routing)
         # set by a kernel whose bounded wait ran out (one word per engine: a fault is seen by the engine it spoiled)
@@ -131,7 +132,7 @@ class Engine:
             use_graphs = os.environ.get("TQ_NO_GRAPHS", "") in ("", "0")
         # a part that cannot run inside a captured step (it says so itself) keeps the whole model out of graphs
         self.graphs = DecodeGraphs(self) if use_graphs and model.capturable() else None
-        self._stateless = all(n is None for n in model.state_needs())
+        self._stateless = all(n is None for n in model.state_needs()) and self.cache.embed_state is None
         # TQ_DEBUG_LAYERS=1 (or =all): every step prints the residual stream's sum and sum of magnitudes after each
         # layer, for positions 0 and 1 (or all), in the manner of the reference's TQ_DEBUG_PREFILL
         # (src/engine/tq_transformer.c:2827-2831); such steps run outside the CUDA graphs
@@ -263,7 +264,7 @@ class Engine:
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=int(want.size),
             max_q_len=int(q_lens.max()), max_kv_len=int((starts + q_lens).max()), act_dtype=self.act_dtype,
             device=self.device, host_q_lens=[int(n) for n in q_lens], host_slots=[int(s) for s in slots],
-            debug=self.debug, status=self.status)
+            debug=self.debug, status=self.status, embed_state=self.cache.embed_state)
         return ctx, dev_tables
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -22,13 +22,16 @@ from typing import Dict
 import numpy as np
 
 
+SPARE_REQUESTS = 64
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                    help="most tokens live requests hold at any time, padding not counted")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -40,7 +43,10 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype, args.device)
-    engine = Engine(model, max_tokens=args.max_tokens, device=args.device)
+    # the cache holds whole pages: every live request may leave most of its last page unused, so room for
+    # that is added for up to SPARE_REQUESTS requests on top of the tokens named
+    from ..cache.paged import PAGE_SIZE
+    engine = Engine(model, max_tokens=args.max_tokens + SPARE_REQUESTS * PAGE_SIZE, device=args.device)
     live: Dict[str, object] = {}
     for line in sys.stdin:
         line = line.strip()

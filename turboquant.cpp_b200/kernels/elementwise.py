@@ -7,7 +7,7 @@ from typing import Optional
 import torch
 
 from ..csrc.build import load_kernel
-from ._call import check, code, ptr, stream, want_f32, want_int32
+from ._call import KernelError, check, code, ptr, stream, want_f32, want_int32
 
 _LIB = "elementwise"
 
@@ -75,3 +75,75 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, out: torch
     check(_LIB, lib.tq_gather_rows(ptr(src), ptr(index), c_int(divisor), ptr(out), c_int(code(out.dtype)),
                                    c_int(R), c_int(H), c_int(src.shape[0]), stream()))
     return out
+
+
+def embed_pair_rows(tokens: torch.Tensor, table: torch.Tensor, pair: Optional[torch.Tensor], scale: float,
+                    buckets: int, mul_prev: int, mul_cur: int, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
+                    seq_start: torch.Tensor, slots: torch.Tensor, last_token: Optional[torch.Tensor],
+                    out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tok] * scale + pair[(prev * mul_prev + tok * mul_cur) mod buckets] as float32; a sequence's
+    first token takes row `buckets` of the pair table.  last_token int32 [max_slots]: each sequence's last token
+    so far, read for a step's first token and renewed by the same launch."""
+    want_int32(tokens, "tokens")
+    want_f32(out, "the residual stream")
+    if pair is not None:
+        want_int32(last_token, "the last tokens")
+        if pair.dtype != table.dtype:
+            raise KernelError("the pair table must have the embedding table's dtype")
+    T, H = out.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_embed_pair_rows(ptr(tokens), ptr(table), ptr(pair), c_int(code(table.dtype)), ptr(out), c_int(T),
+                                       c_int(H), c_int(table.shape[0]), c_float(scale), c_int(buckets),
+                                       c_longlong(mul_prev), c_longlong(mul_cur), ptr(seq_of_token), ptr(cu_seqlens),
+                                       ptr(seq_start), ptr(slots), ptr(last_token), c_int(cu_seqlens.shape[0] - 1),
+                                       stream()))
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += y / sqrt(mean(y^2) + eps) * weight, row by row in float32 (the norm sits on the sub-layer's output);
+    `copy` receives the new x in its own dtype."""
+    want_f32(x, "the residual stream")
+    R, H = x.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_add_rmsnorm(ptr(x), ptr(y), c_int(code(y.dtype)), ptr(weight), c_int(code(weight.dtype)),
+                                   ptr(copy), c_int(code(copy.dtype) if copy is not None else 0), c_int(R), c_int(H),
+                                   c_float(eps), stream()))
+    return x
+
+
+MAP_COPY, MAP_RELU_SQUARED = 0, 1
+
+
+def map_elements(src: torch.Tensor, out: torch.Tensor, function: int = MAP_COPY) -> torch.Tensor:
+    """out = f(src) element by element, computed in float32 and rounded to out's dtype."""
+    if src.numel() != out.numel():
+        raise KernelError("map_elements: sizes differ")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_map(ptr(src), c_int(code(src.dtype)), ptr(out), c_int(code(out.dtype)), c_longlong(src.numel()),
+                           c_int(function), stream()))
+    return out
+
+
+def rotate_pairs(x: torch.Tensor, freq: torch.Tensor, positions: torch.Tensor, mag: float, offset: int = 0) -> None:
+    """Turns the pairs (2i, 2i+1), i < len(freq), from element `offset` of every head of x [T, heads, d] in place
+    by angle position * freq[i] (float32); cos and sin carry the factor `mag`.  x may be a view whose last
+    dimension is dense."""
+    want_f32(freq, "frequencies")
+    want_int32(positions, "positions")
+    T, heads, d = x.shape
+    if x.stride(2) != 1 or offset + 2 * freq.shape[0] > d:
+        raise KernelError("rotate_pairs: heads must be dense and hold the rotated pairs")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_rotate_pairs(ctypes_ptr(x), c_int(code(x.dtype)), ptr(freq), ptr(positions), c_int(T), c_int(heads),
+                                    c_int(x.stride(1)), c_longlong(x.stride(0)), c_int(offset), c_int(freq.shape[0]),
+                                    c_float(mag), stream()))
+
+
+def ctypes_ptr(t: torch.Tensor):
+    """Pointer to the first element of a CUDA tensor that may be a strided view."""
+    import ctypes
+    if not t.is_cuda:
+        raise KernelError("kernels take CUDA tensors; there is no CPU path")
+    return ctypes.c_void_p(t.data_ptr())

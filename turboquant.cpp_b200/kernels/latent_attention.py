@@ -1,0 +1,74 @@
+"""Launchers of csrc/latent_attention.cu: attention over a cache of one latent row per position."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_kernel
+from ._call import KernelError, check, code, ptr, stream, want_f32, want_int32
+
+_LIB = "latent_attention"
+MAX_ROW = 1024       # csrc/latent_attention.cu LAT_MAX_ROW
+HEADS_PER_BLOCK = 4  # csrc/latent_attention.cu LAT_HG
+
+
+def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
+                   freq: Optional[torch.Tensor], mag: float, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   page_table: Optional[torch.Tensor], page_size: int, cache: Optional[torch.Tensor], heads: int,
+                   q_off: int, rot: int, kv_rank: int) -> None:
+    """q [T, heads * q_dim] (activation dtype): the `rot` elements from q_off of every head turn in place.
+    dkv float32 [T, kv_rank + rot] (or None for a layer that reads another layer's cache): its first kv_rank
+    elements are normed (RMS, weight), its last rot turned, and the row is written to the token's place in
+    cache [pages, 1, 1, page_size, kv_rank + rot]."""
+    T = q.shape[0]
+    q_dim = q.shape[1] // heads
+    n_pairs = 0 if freq is None else freq.shape[0]
+    if dkv is not None:
+        want_f32(dkv, "the latent projection")
+        if dkv.shape != (T, kv_rank + rot) or cache is None or cache.dtype != q.dtype:
+            raise KernelError("latent_prepare: the projection, the cache and the queries do not fit together")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_latent_prepare(
+        ptr(q), c_int(code(q.dtype)), ptr(dkv), ptr(norm_weight),
+        c_int(code(norm_weight.dtype) if norm_weight is not None else 0), c_float(eps), ptr(freq), c_float(mag),
+        ptr(positions), ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1] if page_table is not None else 0),
+        c_int(page_size), ptr(cache) if dkv is not None else None, c_int(T), c_int(heads), c_int(q_dim), c_int(q_off),
+        c_int(rot), c_int(n_pairs), c_int(kv_rank), c_int(page_table.shape[0] if page_table is not None else 0),
+        c_int(cache.shape[0] if cache is not None else 0), stream()))
+
+
+def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:
+    """Key ranges per token so that a step of few tokens still fills the GPU: none for prompts, up to 32 for
+    single tokens over long ranges.  The ranges are joined in range order, so a launch shape gives the same bits
+    every time; logits agree across shapes to rounding."""
+    blocks = n_tokens * -(-heads // HEADS_PER_BLOCK)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    if blocks >= 2 * sms or longest < 256:
+        return 1
+    return int(max(1, min(32, (2 * sms) // blocks, longest // 128)))
+
+
+def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: torch.Tensor, sink: Optional[torch.Tensor],
+                     positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
+                     window: int, scale: float, out: torch.Tensor, heads: int, kv_rank: int, rot: int,
+                     n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q_lat [T, heads, kv_rank]: the queries carried into the latent space; q [T, heads * q_dim]: its `rot`
+    elements from q_off of every head meet the rows' last rot elements.  out [T, heads, kv_rank]: the
+    softmax-weighted sums of the rows' first kv_rank elements (sink [heads] float32 joins the denominator)."""
+    T = q_lat.shape[0]
+    if sink is not None:
+        want_f32(sink, "sinks")
+    want_int32(positions, "positions")
+    if cache.dtype != q_lat.dtype or out.dtype != q_lat.dtype or q.dtype != q_lat.dtype:
+        raise KernelError("latent_attention: queries, cache and output must share a dtype")
+    if n_splits > 1 and (partial is None or partial.numel() < T * heads * n_splits * (kv_rank + 2)):
+        raise KernelError("latent_attention: the scratch buffer is too small for the key ranges")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_latent_attention(
+        ptr(q_lat), ptr(q), c_int(q.shape[1] // heads), c_int(q_off), ptr(cache), c_int(code(q_lat.dtype)), ptr(sink),
+        ptr(positions), ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(window),
+        c_float(scale), ptr(out), ptr(partial), c_int(n_splits), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot),
+        c_int(page_table.shape[0]), c_int(cache.shape[0]), stream()), kernels=2 if n_splits > 1 else 1)
+    return out

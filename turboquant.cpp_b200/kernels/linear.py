@@ -52,3 +52,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if out_dtype is not None and y.dtype != out_dtype:
         y = y.to(out_dtype)
     return y
+
+
+def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = x[b] @ weight[b] for every b, the library's strided batched product: x [B, T, K], weight [B, K, N],
+    out [B, T, N]; all three may be views (a dense innermost dimension is enough for the library to take them
+    without a copy).  float32 operands give a true float32 product."""
+    if not x.is_cuda:
+        raise KernelError("batched_linear: CUDA tensors only; there is no CPU path")
+    if x.dtype != weight.dtype or out.dtype != x.dtype:
+        raise KernelError("batched_linear: operands and output must share a dtype")
+    with _FullPrecision():
+        torch.bmm(x, weight, out=out)
+    return out

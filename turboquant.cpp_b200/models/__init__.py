@@ -1,3 +1,4 @@
 """Models: the generic decoder and the architectures built on it."""
-from .decoder import DecoderModel, Embedding, LMHead, ScheduleEntry
+from .decoder import DecoderModel, Embedding, LMHead, PairEmbedding, ScheduleEntry
 from .qwen2_moe import Qwen2MoeModel
+from .nuforax import NuforaxModel

@@ -48,6 +48,55 @@ class Embedding(Part):
         x = torch.empty((tokens.shape[0], self.hidden), dtype=torch.float32, device=tokens.device)
         return K.embed_rows(tokens, self.table, x)
 
+    def state_need(self) -> Optional[StateNeed]:
+        """Per-sequence state the embedding keeps (the step hands it over as ctx.embed_state), or None."""
+        return None
+
+    def embed(self, ctx: StepContext) -> torch.Tensor:
+        """The residual stream's first value for the step's tokens."""
+        return self.forward(ctx.tokens)
+
+
+class PairEmbedding(Embedding):
+    """x = table[token] * scale + pairs[(previous * mul_prev + token * mul_cur) mod buckets]; a sequence's first
+    token takes the pair table's last row (row `buckets`).  The token before a step's first token is the
+    sequence's state: one int32 per slot, kept on the device and renewed by the same launch that reads it."""
+
+    def __init__(self, name: str, vocab: int, hidden: int, scale: float = 1.0, pair_name: Optional[str] = None,
+                 buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0):
+        super().__init__(name, vocab, hidden)
+        if pair_name is not None and buckets < 1:
+            raise ValueError(f"embedding '{name}': a pair table needs at least one bucket, got {buckets}")
+        self.scale, self.pair_name = float(scale), pair_name
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.pairs: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = super().weight_specs()
+        if self.pair_name is not None:
+            specs.append(WeightSpec(self.pair_name, (self.buckets + 1, self.hidden)))
+        return specs
+
+    def bind(self, store: WeightStore) -> None:
+        super().bind(store)
+        if self.pair_name is not None:
+            self.pairs = store.get(self.pair_name).to(self.table.dtype)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((1,), torch.int32) if self.pair_name is not None else None
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError("an embedding that looks at the token before needs the step: use embed(ctx)")
+
+    def embed(self, ctx: StepContext) -> torch.Tensor:
+        x = torch.empty((ctx.tokens.shape[0], self.hidden), dtype=torch.float32, device=ctx.tokens.device)
+        last = ctx.embed_state
+        if self.pairs is not None and last is None:
+            raise RuntimeError("the step brought no state for the embedding's pair table")
+        return K.embed_pair_rows(ctx.tokens, self.table, self.pairs, self.scale, self.buckets, self.mul_prev,
+                                 self.mul_cur, ctx.seq_of_token, ctx.cu_seqlens, ctx.seq_start, ctx.slots,
+                                 None if last is None else last.view(-1), x)
+
 
 class LMHead(Part):
     """logits = W x in float32; ``name`` may be the embedding's tensor (tied weights:
@@ -128,6 +177,9 @@ class DecoderModel:
     def state_needs(self) -> List[Optional[StateNeed]]:
         return [self.blocks[e.block].state_need() for e in self.schedule]
 
+    def embedding_state_need(self) -> Optional[StateNeed]:
+        return self.embedding.state_need() if hasattr(self.embedding, "state_need") else None
+
     def capturable(self) -> bool:
         """Whether decode steps can be recorded into CUDA graphs: every block says so of its own parts."""
         return all(b.capturable() for b in self.blocks)
@@ -150,14 +202,17 @@ class DecoderModel:
     def forward(self, ctx: StepContext, layer_caches: Sequence[LayerCache]) -> Optional[torch.Tensor]:
         """Runs the step's tokens through the schedule; float32 logits [n_want, vocab] (None if
         nothing is wanted)."""
-        x = self.embedding.forward(ctx.tokens)
+        x = self.embedding.embed(ctx) if hasattr(self.embedding, "embed") else self.embedding.forward(ctx.tokens)
         pending = None
         dump = ctx.debug.get("layer_sums") if ctx.debug is not None else None
+        keep = ctx.debug.get("layer_streams") if ctx.debug is not None else None     # tests: the stream after each layer
         for i, (e, cache) in enumerate(zip(self.schedule, layer_caches)):
             x, pending = self.blocks[e.block].forward(x, pending, ctx, cache)
             if dump is not None:             # sum and sum of magnitudes of the residual stream after this layer
                 full = x if pending is None else x + pending.float()
                 dump.append((i, full.sum(dim=1, dtype=torch.float64), full.abs().sum(dim=1, dtype=torch.float64)))
+            if keep is not None:
+                keep.append(x.clone() if pending is None else x + pending.float())
         if ctx.n_want == 0:
             return None
         xn = self.final_norm.forward(x, ctx.act_dtype, rows=ctx.want_rows, add=pending)

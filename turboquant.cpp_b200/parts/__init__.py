@@ -4,8 +4,10 @@ from .base import (KVNeed, StateNeed, LayerCache, StepContext, Part, Norm, Posit
                    make_mixer, make_feed_forward, make_norm, make_position_encoding,
                    MIXERS, FEED_FORWARDS, NORMS, POSITION_ENCODINGS)
 from .norm import RMSNorm
-from .rotary import RotaryEncoding
+from .rotary import RotaryEncoding, ScaledRotaryEncoding
 from .attention import AttentionMixer
-from .dense_ffn import SwiGLUFeedForward
+from .latent_attention import LatentAttentionMixer
+from .ssm import Mamba2Mixer
+from .dense_ffn import SwiGLUFeedForward, ReluSquaredFeedForward
 from .moe_ffn import MoEFeedForward
-from .block import PreNormBlock
+from .block import PreNormBlock, PostNormBlock

@@ -16,7 +16,8 @@ attention or recurrent mixer :2517-2551 and of MoE or dense feed-forward
 Interfaces
 ----------
 Part            weight_specs() -> [WeightSpec]; bind(store); kernels() -> names of kernel files
-Norm            forward(x, out_dtype, rows, add) -> xn; add_forward(x, y) -> xn (x += y in fp32, then the norm)
+Norm            forward(x, out_dtype, rows, add) -> xn; add_forward(x, y) -> xn (x += y in fp32, then the norm);
+                add_normed(x, y, copy) (x += norm(y))
 PositionEncoding  tables() -> (cos, sin, pairing) or None; apply(q, k, positions)
 Mixer           cache_need() -> KVNeed | None; state_need() -> StateNeed | None; capturable() -> bool;
                 forward(xn, ctx, cache) -> y [T, hidden]
@@ -48,6 +49,7 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2          # tensors kept per position: 2 (keys and values), or 1 (one row that serves as both)
 
 
 @dataclass(frozen=True)
@@ -60,7 +62,7 @@ class StateNeed:
 @dataclass
 class LayerCache:
     """What one entry of the layer schedule sees of the cache during a step."""
-    kv: Optional[torch.Tensor] = None            # [pages, 2, n_kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor] = None            # [pages, planes, n_kv_heads, page_size, head_dim]
     page_table: Optional[torch.Tensor] = None    # [n_seqs, width] int32, the group's pages per sequence
     page_size: int = 0
     writes: bool = True                          # False: reads another entry's cache, writes nothing
@@ -90,6 +92,7 @@ class StepContext:
     host_slots: Sequence[int] = ()
     debug: Optional[Dict[str, Any]] = None      # tests: parts may record what they decided
     status: Optional[torch.Tensor] = None       # int32 [1]: kernels with bounded waits report here when one ran out
+    embed_state: Optional[torch.Tensor] = None  # [max_slots, *shape]: the embedding's per-sequence state, if it keeps one
 
 
 class Part:
@@ -119,6 +122,11 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_forward(self, x: torch.Tensor, y: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_normed(self, x: torch.Tensor, y: torch.Tensor, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x += norm(y) in fp32, for blocks whose norms sit on the sub-layers' outputs; `copy` receives the new x
+        in its own dtype."""
         raise NotImplementedError
 
 

@@ -49,3 +49,54 @@ class PreNormBlock(Block):
         y = self.mixer.forward(xn, ctx, cache)
         xn = self.ffn_norm.add_forward(x, y, ctx.act_dtype)
         return x, self.ffn.forward(xn, ctx)
+
+
+class PostNormBlock(Block):
+    """x += norm(mixer(x)); x += norm(feed_forward(x)): the sub-layers read the residual stream itself and the
+    norms sit on their outputs.  The feed-forward (and its norm) may be absent.  The stream stays float32; the
+    sub-layers read it rounded to the activation dtype, and the first sum writes that copy for the second
+    sub-layer in the same pass."""
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: Optional[FeedForward] = None, ffn_norm: Optional[Norm] = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+
+    def parts(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    def cache_need(self) -> Optional[KVNeed]:
+        return self.mixer.cache_need()
+
+    def state_need(self) -> Optional[StateNeed]:
+        return self.mixer.state_need()
+
+    def capturable(self) -> bool:
+        return self.mixer.capturable() and (self.ffn is None or self.ffn.capturable())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self.parts() for s in p.weight_specs()]
+
+    def bind(self, store: WeightStore) -> None:
+        for p in self.parts():
+            p.bind(store)
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"] + [k for p in self.parts() for k in p.kernels()]
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        from ..kernels import elementwise as K
+        if pending is not None:                      # a block of another kind ran before and left its sum open
+            K.residual_add(x, pending)
+        exact = ctx.act_dtype == torch.float32
+        h = x if exact else K.map_elements(x, torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device))
+        y = self.mixer.forward(h, ctx, cache)
+        if self.ffn is None:
+            self.mixer_norm.add_normed(x, y)
+            return x, None
+        h = None if exact else torch.empty(x.shape, dtype=ctx.act_dtype, device=x.device)
+        self.mixer_norm.add_normed(x, y, copy=h)
+        y = self.ffn.forward(x if exact else h, ctx)
+        self.ffn_norm.add_normed(x, y)
+        return x, None

@@ -46,3 +46,38 @@ class SwiGLUFeedForward(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLUFeedForward)
+
+
+class ReluSquaredFeedForward(FeedForward):
+    """down(relu(up x)^2): one product up, the square of relu, one product down."""
+
+    def __init__(self, prefix: str, hidden: int, intermediate: int, up_name: str = "up", down_name: str = "down"):
+        if hidden < 1 or intermediate < 1:
+            raise ValueError(f"feed-forward '{prefix}': sizes must be positive, got {hidden}, {intermediate}")
+        self.prefix, self.hidden, self.intermediate = prefix, int(hidden), int(intermediate)
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p = self.prefix
+        return [WeightSpec(p + self.up_name, (self.intermediate, self.hidden)),
+                WeightSpec(p + self.down_name, (self.hidden, self.intermediate))]
+
+    def bind(self, store: WeightStore) -> None:
+        self.w_up, self.w_down = store.get(self.prefix + self.up_name), store.get(self.prefix + self.down_name)
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"]
+
+    def step_work(self, n_tokens, kv_tokens):
+        wb = lambda w: 0 if w is None else w.numel() * w.element_size()
+        return {"matmul": (wb(self.w_up) + wb(self.w_down), 4.0 * n_tokens * self.hidden * self.intermediate)}
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        u = linear(xn, self.w_up, out_dtype=torch.float32)          # fp32 until the activation has been taken
+        h = torch.empty((xn.shape[0], self.intermediate), dtype=ctx.act_dtype, device=xn.device)
+        K.map_elements(u, h, K.MAP_RELU_SQUARED)
+        return linear(h, self.w_down, out_dtype=torch.float32)
+
+
+register_feed_forward("relu2", ReluSquaredFeedForward)

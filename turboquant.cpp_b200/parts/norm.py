@@ -36,5 +36,8 @@ class RMSNorm(Norm):
         out = torch.empty((x.shape[0], self.size), dtype=out_dtype, device=x.device)
         return K.rmsnorm(x, self.weight, self.eps, out, add=y)
 
+    def add_normed(self, x, y, copy=None):
+        return K.add_rmsnorm(x, y, self.weight, self.eps, copy)
+
 
 register_norm("rmsnorm", RMSNorm)

@@ -7,6 +7,7 @@ powf/cosf/sinf for every head of every token; here cos and sin are float32 table
 built once (angles in float64, rounded once to float32)."""
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -40,3 +41,55 @@ class RotaryEncoding(PositionEncoding):
 
 
 register_position_encoding("rotary", RotaryEncoding)
+
+
+class ScaledRotaryEncoding(PositionEncoding):
+    """Rotation of interleaved pairs (2i, 2i+1), i < dims/2, with frequencies stretched for contexts longer than
+    the one trained on: with f_i = base^(-2i/dims) and, for a number of turns t over the original context,
+    pair(t) = dims * ln(original / (2 pi t)) / (2 ln base), the pairs below lo = max(floor(pair(fast)), 0) keep
+    f_i, the pairs above hi = min(ceil(pair(slow)), dims - 1) take f_i / factor, and between them the two are
+    mixed by ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1).  cos and sin are multiplied by
+    0.1 ln(factor) + 1.  Without a factor it is the plain interleaved rotation.
+
+    There is no table over positions and so no longest position: kernels compute angle = position * frequency
+    in float32 from the frequencies (`freq`, float32 [dims/2] on the device) and the factor `mag`."""
+
+    def __init__(self, dims: int, base: float, factor: Optional[float] = None, original: float = 0.0,
+                 fast: float = 0.0, slow: float = 0.0):
+        if dims % 2 or dims < 0:
+            raise ValueError(f"rotary: {dims} rotated dimensions must be even")
+        if not base > 0:
+            raise ValueError(f"rotary: base {base} must be positive")
+        self.dims, self.base = int(dims), float(base)
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / max(self.dims, 1))
+        self.mag = 1.0
+        if factor is not None:
+            if not (factor > 0 and original > 0 and fast > 0 and slow > 0):
+                raise ValueError("rotary: factor, original, fast and slow must be positive")
+            pair = lambda turns: self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(pair(fast)), 0)
+            hi = min(math.ceil(pair(slow)), self.dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            self.mag = 0.1 * math.log(factor) + 1.0
+        self._freq64 = f
+        self.freq: Optional[torch.Tensor] = None
+
+    def prepare(self, device) -> None:
+        if self.freq is None or self.freq.device != torch.device(device):
+            self.freq = self._freq64.to(torch.float32).to(device).contiguous()
+
+    def kernels(self):
+        return ["elementwise"]
+
+    def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], positions: torch.Tensor) -> None:
+        from ..kernels import elementwise as K
+        if self.dims == 0:
+            return
+        K.rotate_pairs(q, self.freq, positions, self.mag)
+        if k is not None:
+            K.rotate_pairs(k, self.freq, positions, self.mag)
+
+
+register_position_encoding("rotary_scaled", ScaledRotaryEncoding)
