@@ -150,7 +150,13 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
                     "prefill to this file (torch profiler; not part of any timed number)")
+    ap.add_argument("--design", choices=["nuforax"], default="", help="instead of the default workload: prompt and decode "
+                    "speed of this design at layer sizes of a real model (random weights), beside the dense Qwen2 decoder of "
+                    "equal width, depth and heads")
+    ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of the sizes to run")
     args = ap.parse_args()
+    if args.design and args.impl != "reference":
+        return design_compare(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a C project without setup.py/pyproject.toml at its root (pip install fails), "
@@ -315,10 +321,155 @@ def main() -> int:
     return 0
 
 
-def kernel_table(tq, model, rng, V, batch, path):
+# ---- another design beside the closest existing model ------------------------------------------------------------
+def nuforax_config(width, layers, heads, dim, rot, vdim, rank, window, ff, m_heads, m_vdim, m_state, m_groups, vocab):
+    """Layers in threes: latent attention, latent attention reading the first one's rows, state-space mixer."""
+    rot_cfg = {"base": 1000000.0, "dims": rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    att = lambda src: {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff}, "mixer": dict(
+        {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+         "mask": {"size": window}, "rot": rot_cfg}, **({} if src is None else {"kv_from": src}))}
+    ssm = {"type": "mamba2", "mlp": None, "mixer": {"heads": m_heads, "vdim": m_vdim, "state": m_state, "groups": m_groups,
+                                                    "conv": 4, "norm_groups": m_groups}}
+    out = []
+    for i in range(layers):
+        out.append(att(None) if i % 3 == 0 else att(i - 1) if i % 3 == 1 else ssm)
+    return {"architecture": "Nuforax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+
+
+def dense_qwen2_config(width, layers, heads, window, inter, vocab):
+    return dict(A27B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=max(1, heads // 4),
+                head_dim=128, num_experts=0, num_experts_per_tok=0, moe_intermediate_size=0, shared_expert_intermediate_size=0,
+                intermediate_size=inter, vocab_size=vocab, use_sliding_window=True, sliding_window=window, max_window_layers=0,
+                max_position_embeddings=8192, tie_word_embeddings=True)
+
+
+DESIGN_SIZES = {
+    # name: (width, layers, heads, dim, rot, vdim, rank, window, ff, ssm heads, ssm vdim, ssm state, ssm groups, vocab)
+    "w1024": (1024, 6, 8, 64, 32, 64, 256, 1024, 4096, 32, 64, 64, 1, 32768),
+    "w2048": (2048, 6, 16, 128, 64, 128, 512, 1024, 8192, 64, 64, 128, 8, 32768),
+}
+
+
+def design_compare(args) -> int:
+    """Prompt and decode speed of the Nuforax decoder and of the dense Qwen2 decoder of equal width, depth, heads and
+    window (its feed-forward sized to the same number of weights), timed on the device with CUDA events."""
+    import numpy as np
+    import torch
+    import turboquant_cpp_b200 as tq
+    from turboquant_cpp_b200.kernels import _call
+    if args.gpus != 1:
+        print(json.dumps({"error": "one GPU only", "n_gpus": args.gpus}))
+        return 2
+    pk = peaks()
+    rng = np.random.default_rng(0)
+    steps, warmup = max(8, min(args.steps, 32)), max(3, args.warmup)
+    prompt = 2048
+
+    def weights_bytes(model):
+        seen, total = set(), 0
+        for spec in model.weight_specs():
+            if spec.name not in seen:
+                seen.add(spec.name)
+                n = 1
+                for d in spec.shape:
+                    n *= d
+                total += 2 * n
+        return total
+
+    def measure(model, V):
+        out = {"weights_gb": round(weights_bytes(model) / 1e9, 3)}
+        eng = tq.Engine(model, max_tokens=prompt + 64, max_slots=1)
+        toks = rng.integers(0, V, size=prompt).tolist()
+        best = float("inf")
+        for i in range(4):
+            s = eng.open()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            eng.step([tq.StepEntry(s, toks, [prompt - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            if i > 0:
+                best = min(best, a.elapsed_time(b))
+            eng.close(s)
+        eng.release()
+        out["prefill_2048"] = {"ms": round(best, 3), "tokens_per_s": round(prompt / best * 1e3, 1)}
+        for batch in (1, 8, 64):
+            eng = tq.Engine(model, max_tokens=batch * (prompt + 128), max_slots=batch)
+            seqs = [eng.open() for _ in range(batch)]
+            for g0 in range(0, batch, 8):
+                eng.step([tq.StepEntry(s, rng.integers(0, V, size=prompt).tolist(), []) for s in seqs[g0:g0 + 8]])
+            toks = rng.integers(0, V, size=(warmup + steps, batch))
+            one = lambda i: eng.step([tq.StepEntry(s, [int(toks[i, j])], [0]) for j, s in enumerate(seqs)])
+            for i in range(warmup):
+                one(i)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = _call.LAUNCHES
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(warmup, warmup + steps):
+                one(i)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            out[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1),
+                                       "launches_per_step": (_call.LAUNCHES - l0) // steps,
+                                       # every weight once per step against the measured copy bandwidth
+                                       "weights_frac_of_copy_peak": round(weights_bytes(model) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            for s in seqs:
+                eng.close(s)
+            eng.release()
+            del eng
+            gc.collect()
+            torch.cuda.empty_cache()
+        return out
+
+    result = {"metric": "prompt and decode speed, Nuforax beside the dense Qwen2 decoder of equal width", "unit": "tokens/s",
+              "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+              "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.sizes.split(","):
+        if name not in DESIGN_SIZES:
+            print(json.dumps({"error": f"unknown size '{name}'; known: {sorted(DESIGN_SIZES)}"}))
+            return 2
+        (W, L, H, dim, rot, vdim, rank, window, ff, mh, mv, mn, mg, V) = DESIGN_SIZES[name]
+        cfg = nuforax_config(W, L, H, dim, rot, vdim, rank, window, ff, mh, mv, mn, mg, V)
+        model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry = {"nuforax": dict(measure(model, V), config={"width": W, "layers": L, "heads": H, "dim": dim, "rot_dim": rot,
+                                                             "vdim": vdim, "kv_rank": rank, "window": window, "ff": ff,
+                                                             "ssm": {"heads": mh, "vdim": mv, "state": mn, "groups": mg}})}
+        if args.kernel_table:
+            kernel_table(tq, model, rng, V, 8, args.kernel_table + f".nuforax_{name}.txt", prompt=prompt, context=prompt + 128)
+        nbytes = weights_bytes(model)
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+        # the sibling's feed-forward takes up the weights the other design spends elsewhere, so both stream equal bytes
+        qcfg = dense_qwen2_config(W, L, H, window, 64, V)
+        base = weights_bytes(tq.build_model(qcfg, "bfloat16"))
+        inter = max(64, int(round((nbytes - base) / 2 / (3 * W * L) / 64.0)) * 64 + 64)
+        qcfg = dense_qwen2_config(W, L, H, window, inter, V)
+        model = tq.random_model(qcfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry["qwen2_dense"] = dict(measure(model, V), config={"width": W, "layers": L, "heads": H, "kv_heads": max(1, H // 4),
+                                                               "head_dim": 128, "window": window, "intermediate": inter})
+        if args.kernel_table:
+            kernel_table(tq, model, rng, V, 8, args.kernel_table + f".qwen2_{name}.txt", prompt=prompt, context=prompt + 128)
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+        result["sizes"][name] = entry
+    result["clocks"] = clocks.stop()
+    print(json.dumps(result))
+    return 0
+
+
+def kernel_table(tq, model, rng, V, batch, path, prompt=None, context=None):
     """Per-kernel device time of 4 decode steps at context 2,048 and of one 2,048-token prefill."""
     import torch
     from torch.profiler import ProfilerActivity, profile
+    PROMPT, CONTEXT = prompt or globals()["PROMPT"], context or globals()["CONTEXT"]
     eng = tq.Engine(model, max_tokens=batch * CONTEXT, max_slots=batch)
     seqs = [eng.open() for _ in range(batch)]
     for g0 in range(0, batch, 8):

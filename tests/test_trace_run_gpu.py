@@ -97,7 +97,11 @@ def test_nothing_wanted_writes_nothing_and_cache_full_is_an_error(tiny_folders, 
     folder = tiny_folders["A"]
     got = replay(folder, "float32", [[("a", [1, 2, 3], [])], [("a", [4], [0])]], {1: ["a"]}, str(tmp_path / "o"))
     assert sorted(got["a"]) == [3]
-    lines = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": list(range(100)), "want": []}], "end": []})
+    # --max-tokens counts tokens, not the unused rest of every request's last page: the cache keeps spare pages for
+    # that, so the error comes when the requests need more pages than the tokens named plus the spare ones
+    from turboquant_cpp_b200.engine.trace import SPARE_REQUESTS
+    lines = json.dumps({"step": 0, "entries": [{"id": f"r{i}", "tokens": [1], "want": []} for i in range(SPARE_REQUESTS + 6)],
+                        "end": []})
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
                         "--out", str(tmp_path / "o2"), "--max-tokens", "64"], input=lines + "\n",
                        capture_output=True, text=True, timeout=600)

@@ -146,11 +146,11 @@ class NuforaxConfig:
             if l.type == "latent_attention" and l.mixer.kv_from is not None:
                 j = l.mixer.kv_from
                 if not 0 <= j < i or layers[j].type != "latent_attention" or layers[j].mixer.kv_from is not None:
-                    raise ConfigError(f"{where}: layers[{i}] takes its keys from layer {j}, which must be an earlier "
+                    raise ConfigError(f"{where}: layers[{i}]: mixer 'kv_from' names layer {j}, which must be an earlier "
                                       f"latent_attention layer with a projection of its own")
                 a, b = l.mixer, layers[j].mixer
                 if (a.kv_rank, a.rot_dim) != (b.kv_rank, b.rot_dim):
-                    raise ConfigError(f"{where}: layers[{i}] and the layer it takes its keys from differ in "
+                    raise ConfigError(f"{where}: layers[{i}] and layer {j}, which its 'kv_from' names, differ in "
                                       f"kv_rank or rot_dim")
         return cls(vocab=r.integer("vocab", minimum=1), width=width, eps=_sub(r, "norm").real("eps", positive=True),
                    embedding_scale=scale, pair_table=pair, layers=tuple(layers), raw=dict(raw),

@@ -9,6 +9,9 @@
 //   latent_prepare    norm of the latent, rotation of kr and of the queries' rotated part, cache write
 //   latent_attention  scores, softmax with an optional sink per head, weighted sum of latents
 //   latent_merge      joins the key ranges of a split launch
+// and, for long runs of new tokens (prompts), where scores and sums are matrix products of the library,
+//   latent_gather     a range of one sequence's rows from the pages into a dense matrix
+//   latent_softmax    rows of scores -> weights: mask (causal, window), scale, softmax with the sink
 // Scores, softmax and sums are fp32.  A sink is a learned logit per head that takes part in the softmax's
 // denominator and has no value: out = sum_j e^{s_j - M} c_j / (sum_j e^{s_j - M} + e^{sink - M}).
 // Window w > 0: position i sees j with 0 <= i - j < w.
@@ -307,5 +310,85 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
             (tq_launch(mgrid, 128, 0, stream)(latent_merge_kernel<TA>, (const float*)partial, sink, n_splits, H, R, (TA*)out)));
         TQ_CHECK_LAUNCH("latent_merge");
     }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Prompt path.  out[j] = the row of position k0 + j of one sequence, j < n (16-byte copies when rows allow it).
+// ---------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void latent_gather_kernel(const TA* __restrict__ cache, const int* __restrict__ table, int table_stride,
+                                     int page_size, int k0, int n, int Dk, TA* __restrict__ out, int vec, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int j = blockIdx.x * warps + (threadIdx.x >> 5); j < n; j += gridDim.x * warps) {
+        const int p = k0 + j;
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+        const TA* src = cache + ((size_t)page * page_size + p % page_size) * Dk;
+        TA* dst = out + (size_t)j * Dk;
+        if (vec) {
+            const int n16 = (int)((size_t)Dk * sizeof(TA) / 16);
+            for (int i = lane; i < n16; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        } else {
+            for (int i = lane; i < Dk; i += 32) dst[i] = src[i];
+        }
+    }
+}
+
+TQ_EXPORT int tq_latent_gather(const void* cache, int act_dtype, const int* table, int table_stride, int page_size, int k0,
+                               int n, int Dk, void* out, int n_pages, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TQ_REQUIRE(n > 0 && k0 >= 0 && Dk >= 1, "latent_gather: bad range %d + %d", k0, n);
+    const int esize = act_dtype == TQ_F32 ? 4 : 2;
+    const int vec = ((size_t)Dk * esize) % 16 == 0 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    int blocks = (n + 7) / 8;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    TQ_DISPATCH(act_dtype, TA,
+        (tq_launch(blocks, 256, 0, stream)(latent_gather_kernel<TA>, (const TA*)cache, table, table_stride, page_size, k0, n,
+                                           Dk, (TA*)out, vec, n_pages)));
+    TQ_CHECK_LAUNCH("latent_gather");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// scores [rows, n_keys] fp32 (row r: token r / H of the run, head r % H; column j: position k0 + j) -> weights in
+// the activation dtype: w_j = exp(s_j * scale - M) / (sum_visible exp(s * scale - M) + exp(sink_h - M)), 0 where
+// the token at position pos0 + r / H does not see position k0 + j (later, or window positions or more back).
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void latent_softmax_kernel(const float* __restrict__ scores, const float* __restrict__ sink, float scale,
+                                      int window, int pos0, int k0, int n_keys, int H, TO* __restrict__ weights) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const int h = (int)(r % H), pos = pos0 + (int)(r / H);
+    const int lo = max(window > 0 ? pos + 1 - window : 0, k0) - k0, hi = min(pos + 1 - k0, n_keys);     // visible columns
+    const float* s = scores + r * n_keys;
+    TO* w = weights + r * n_keys;
+    const float sk = sink ? sink[h] : -INFINITY;
+    float m = sk;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) m = fmaxf(m, s[j] * scale);
+    m = tq_block_max(m, scratch);
+    float l = 0.f;
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) l += expf(s[j] * scale - m);
+    l = tq_block_sum(l, scratch);
+    if (sink) l += expf(sk - m);
+    const float inv = 1.0f / l;
+    for (int j = threadIdx.x; j < n_keys; j += blockDim.x)
+        w[j] = tq_from_float<TO>(j >= lo && j < hi ? expf(s[j] * scale - m) * inv : 0.f);
+}
+
+TQ_EXPORT int tq_latent_softmax(const float* scores, const float* sink, float scale, int window, int pos0, int k0,
+                                int n_keys, int H, void* weights, int out_dtype, long long rows, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    TQ_REQUIRE(rows > 0 && rows <= 0x7fffffffLL && n_keys >= 1 && H >= 1 && window >= 0 && k0 >= 0 && pos0 >= k0,
+               "latent_softmax: bad sizes");
+    const int threads = n_keys >= 1024 ? 256 : 128;
+    TQ_DISPATCH(out_dtype, TO,
+        (tq_launch((int)rows, threads, 0, stream)(latent_softmax_kernel<TO>, scores, sink, scale, window, pos0, k0, n_keys, H,
+                                                  (TO*)weights)));
+    TQ_CHECK_LAUNCH("latent_softmax");
     return 0;
 }

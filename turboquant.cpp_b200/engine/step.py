@@ -264,6 +264,7 @@ class Engine:
             seq_start=parts[4], slots=parts[5], want_rows=parts[6], n_want=int(want.size),
             max_q_len=int(q_lens.max()), max_kv_len=int((starts + q_lens).max()), act_dtype=self.act_dtype,
             device=self.device, host_q_lens=[int(n) for n in q_lens], host_slots=[int(s) for s in slots],
+            host_seq_start=[int(s) for s in starts],
             debug=self.debug, status=self.status, embed_state=self.cache.embed_state)
         return ctx, dev_tables
 

@@ -72,3 +72,31 @@ def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: to
         c_float(scale), ptr(out), ptr(partial), c_int(n_splits), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot),
         c_int(page_table.shape[0]), c_int(cache.shape[0]), stream()), kernels=2 if n_splits > 1 else 1)
     return out
+
+
+def latent_gather(cache: torch.Tensor, table_row: torch.Tensor, page_size: int, k0: int, n: int, out: torch.Tensor) -> torch.Tensor:
+    """out[j] = the cached row of position k0 + j of the sequence whose pages table_row lists, j < n."""
+    want_int32(table_row, "the page table")
+    Dk = cache.shape[-1]
+    if out.shape != (n, Dk) or out.dtype != cache.dtype:
+        raise KernelError("latent_gather: the output must be [n, row] in the cache's dtype")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_latent_gather(ptr(cache), c_int(code(cache.dtype)), ptr(table_row), c_int(table_row.shape[0]),
+                                     c_int(page_size), c_int(k0), c_int(n), c_int(Dk), ptr(out), c_int(cache.shape[0]), stream()))
+    return out
+
+
+def latent_softmax(scores: torch.Tensor, sink: Optional[torch.Tensor], scale: float, window: int, pos0: int, k0: int,
+                   heads: int, weights: torch.Tensor) -> torch.Tensor:
+    """scores float32 [tokens * heads, n_keys] of a run of tokens at positions pos0 … against positions k0 …:
+    the softmax of the visible scores (causal, window) times scale, the sink in the denominator; 0 elsewhere."""
+    want_f32(scores, "scores")
+    rows, n_keys = scores.shape
+    if weights.shape != scores.shape:
+        raise KernelError("latent_softmax: weights and scores differ in shape")
+    lib = load_kernel(_LIB)
+    from ctypes import c_longlong
+    check(_LIB, lib.tq_latent_softmax(ptr(scores), ptr(sink), c_float(scale), c_int(window), c_int(pos0), c_int(k0),
+                                      c_int(n_keys), c_int(heads), ptr(weights), c_int(code(weights.dtype)), c_longlong(rows),
+                                      stream()))
+    return weights

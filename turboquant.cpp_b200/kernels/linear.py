@@ -65,3 +65,18 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     with _FullPrecision():
         torch.bmm(x, weight, out=out)
     return out
+
+
+def product(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [T, K] @ w [K, N] through the library, operands as they lie (views with a dense innermost dimension are
+    taken without a copy); float32 operands give a true float32 product, bfloat16 ones accumulate in float32."""
+    if not x.is_cuda:
+        raise KernelError("product: CUDA tensors only; there is no CPU path")
+    if x.dtype != w.dtype:
+        raise KernelError("product: operands must share a dtype")
+    with _FullPrecision():
+        if out is not None:
+            return torch.mm(x, w, out=out)
+        if out_dtype is not None and out_dtype != x.dtype:
+            return torch.mm(x, w, out_dtype=out_dtype)
+        return torch.mm(x, w)

@@ -90,6 +90,7 @@ class StepContext:
     # host copies, for parts that must walk sequences in order (stateful mixers)
     host_q_lens: Sequence[int] = ()
     host_slots: Sequence[int] = ()
+    host_seq_start: Sequence[int] = ()
     debug: Optional[Dict[str, Any]] = None      # tests: parts may record what they decided
     status: Optional[torch.Tensor] = None       # int32 [1]: kernels with bounded waits report here when one ran out
     embed_state: Optional[torch.Tensor] = None  # [max_slots, *shape]: the embedding's per-sequence state, if it keeps one

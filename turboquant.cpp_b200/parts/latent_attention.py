@@ -23,12 +23,15 @@ from typing import List, Optional
 import torch
 
 from ..kernels import latent_attention as KL
-from ..kernels.linear import batched_linear, linear
+from ..kernels.linear import batched_linear, linear, product
 from ..weights.loader import WeightSpec, WeightStore
 from .base import KVNeed, LayerCache, Mixer, StepContext, register_mixer
 
 
 class LatentAttentionMixer(Mixer):
+    PROMPT_MIN_RUN = 32       # steps whose longest run of new tokens is at least this take the matrix-product path
+    PROMPT_ROWS = 8192        # (token, head) rows of scores per block of that path
+
     def __init__(self, prefix: str, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  scale: float, eps: float, window: int = 0, position=None, own_cache: bool = True,
                  keep_window: Optional[int] = None, sink: bool = True):
@@ -106,15 +109,51 @@ class LatentAttentionMixer(Mixer):
             batched_linear(q3[:, :, :self.dim].transpose(0, 1), self.w_uk, q_lat.transpose(0, 1))
         else:
             q_lat.zero_()
-        longest = min(self.window, ctx.max_kv_len) if self.window else ctx.max_kv_len
-        n_splits = KL.splits_for(T, H, longest, xn.device)
-        partial = torch.empty(T * H * n_splits * (R + 2), dtype=torch.float32, device=xn.device) if n_splits > 1 else None
         sums = torch.empty((T, H, R), dtype=act, device=xn.device)
-        KL.latent_attention(q_lat, q, self.dim, cache.kv, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
-                            cache.page_size, self.window, self.scale, sums, H, R, self.rot_dim, n_splits, partial)
+        if ctx.max_q_len >= self.PROMPT_MIN_RUN and len(ctx.host_q_lens) == ctx.n_seqs and len(ctx.host_seq_start) == ctx.n_seqs:
+            self._attend_runs(q3, q_lat, sums, ctx, cache)
+        else:
+            self._attend_tokens(q, q_lat, sums, ctx, cache)
         v = torch.empty((T, H, self.vdim), dtype=act, device=xn.device)
         batched_linear(sums.transpose(0, 1), self.w_uv_t, v.transpose(0, 1))
         return linear(v.view(T, H * self.vdim), self.w_o, out_dtype=torch.float32)
+
+    def _attend_tokens(self, q, q_lat, sums, ctx: StepContext, cache: LayerCache) -> None:
+        """Every token on its own: the kernel walks its keys (decode steps, short runs).  Reads device tensors of
+        the step only, so it runs inside the decode graphs."""
+        T, H, R = q_lat.shape
+        longest = min(self.window, ctx.max_kv_len) if self.window else ctx.max_kv_len
+        n_splits = KL.splits_for(T, H, longest, xn.device)
+        partial = torch.empty(T * H * n_splits * (R + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
+        KL.latent_attention(q_lat, q, self.dim, cache.kv, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
+                            cache.page_size, self.window, self.scale, sums, H, R, self.rot_dim, n_splits, partial)
+
+    def _attend_runs(self, q3, q_lat, sums, ctx: StepContext, cache: LayerCache) -> None:
+        """Long runs of new tokens (prompts): all heads of a block of tokens meet the same cached rows, so scores
+        and weighted sums are two matrix products of the library over (token, head) rows, with the mask, the
+        scale and the softmax with its sink between them in a kernel of their own (float32 scores in, weights in
+        the activation dtype out).  A block's rows are gathered from the pages once.  It walks the step's
+        sequences on the host; steps of single tokens never come here."""
+        H, R, Dk = self.heads, self.kv_rank, self.kv_rank + self.rot_dim
+        act, dev = q_lat.dtype, q_lat.device
+        block = max(16, self.PROMPT_ROWS // H)
+        t0 = 0
+        for i, (n, start) in enumerate(zip(ctx.host_q_lens, ctx.host_seq_start)):
+            for a in range(0, n, block):
+                b = min(n, a + block)
+                pos0, k1 = start + a, start + b
+                k0 = max(0, pos0 + 1 - self.window) if self.window else 0
+                rows = torch.empty((k1 - k0, Dk), dtype=act, device=dev)
+                KL.latent_gather(cache.kv, cache.page_table[i], cache.page_size, k0, k1 - k0, rows)
+                qa = torch.empty((b - a, H, Dk), dtype=act, device=dev)            # [query in the latent space | rotated part]
+                qa[:, :, :R].copy_(q_lat[t0 + a:t0 + b])
+                if self.rot_dim:
+                    qa[:, :, R:].copy_(q3[t0 + a:t0 + b, :, self.dim:])
+                scores = product(qa.view(-1, Dk), rows.t(), out_dtype=torch.float32)
+                weights = torch.empty(scores.shape, dtype=act, device=dev)
+                KL.latent_softmax(scores, self.sink, self.scale, self.window, pos0, k0, H, weights)
+                product(weights, rows[:, :R], out=sums[t0 + a:t0 + b].view(-1, R))
+            t0 += n
 
 
 register_mixer("latent_attention", LatentAttentionMixer)
