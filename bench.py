@@ -346,7 +346,7 @@ def dense_qwen2_config(width, layers, heads, window, inter, vocab):
 
 DESIGN_SIZES = {
     # name: (width, layers, heads, dim, rot, vdim, rank, window, ff, ssm heads, ssm vdim, ssm state, ssm groups, vocab)
-    "w1024": (1024, 6, 8, 64, 32, 64, 256, 1024, 4096, 32, 64, 64, 1, 32768),
+    "w1024": (1024, 6, 8, 64, 64, 64, 256, 1024, 4096, 32, 64, 64, 1, 32768),
     "w2048": (2048, 6, 16, 128, 64, 128, 512, 1024, 8192, 64, 64, 128, 8, 32768),
 }
 

@@ -97,7 +97,7 @@ TQ_EXPORT int tq_latent_prepare(void* q, int act_dtype, const float* dkv, const 
 
 // ---------------------------------------------------------------------------------------
 // latent_attention: grid (tokens, ceil(heads / LAT_HG), n_splits), LAT_WARPS warps.  The block's keys (its share of
-// the token's range) go round the warps; a lane holds EPL elements of the row in groups of VEC neighbours
+// the token's range) go round the warps in groups of neighbours; a lane holds EPL elements of the row in groups of VEC neighbours
 // (element VEC*lane + 32*VEC*j + c), so a warp reads a row with 8- or 16-byte loads; the LAT_HG heads' queries
 // lie in shared memory.  Each warp keeps an online softmax per head; the warps' states are joined through shared
 // memory in warp order.  n_splits == 1: the sink joins and the result is written; otherwise the block's state
@@ -161,37 +161,72 @@ latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, 
 #pragma unroll
         for (int j = 0; j < EPL; ++j) acc[g][j] = 0.f;
     }
-    for (int p = lo + warp; p < hi; p += LAT_WARPS) {
-        const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
-        const TA* kp = cache + ((size_t)page * page_size + p % page_size) * Dk;
-        float kr[EPL];
+    // A warp takes KB neighbouring keys at a time: their rows are asked for together, the KB x LAT_HG scores are
+    // summed over the lanes side by side (independent chains of shuffles), and the online softmax moves once per
+    // group of keys.
+    constexpr int KB = EPL <= 20 ? 4 : 2;
+    for (int p0 = lo + warp * KB; p0 < hi; p0 += LAT_WARPS * KB) {
+        float kr[KB][EPL];
 #pragma unroll
-        for (int j = 0; j < NG; ++j) {
-            const int e = VEC * lane + 32 * VEC * j;
-            if (e < Dk) LatRow<TA, VEC>::load(kp + e, kr + VEC * j);
-            else {
+        for (int b = 0; b < KB; ++b) {
+            const int p = min(p0 + b, hi - 1);           // a group's missing keys repeat its last one and get no weight
+            const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+            const TA* kp = cache + ((size_t)page * page_size + p % page_size) * Dk;
 #pragma unroll
-                for (int c = 0; c < VEC; ++c) kr[VEC * j + c] = 0.f;
+            for (int j = 0; j < NG; ++j) {
+                const int e = VEC * lane + 32 * VEC * j;
+                if (e < Dk) LatRow<TA, VEC>::load(kp + e, &kr[b][VEC * j]);
+                else {
+#pragma unroll
+                    for (int c = 0; c < VEC; ++c) kr[b][VEC * j + c] = 0.f;
+                }
             }
         }
+        float sc[LAT_HG][KB];
 #pragma unroll
         for (int g = 0; g < LAT_HG; ++g) {
-            float s = 0.f;
+#pragma unroll
+            for (int b = 0; b < KB; ++b) sc[g][b] = 0.f;
 #pragma unroll
             for (int j = 0; j < NG; ++j) {
                 const int e = VEC * lane + 32 * VEC * j;
                 if (e < Dk) {
 #pragma unroll
-                    for (int c = 0; c < VEC; ++c) s += qs[g * Dk + e + c] * kr[VEC * j + c];
+                    for (int c = 0; c < VEC; ++c) {
+                        const float qv = qs[g * Dk + e + c];
+#pragma unroll
+                        for (int b = 0; b < KB; ++b) sc[g][b] += qv * kr[b][VEC * j + c];
+                    }
                 }
             }
-            s = tq_warp_sum(s) * scale;
-            const float m_new = fmaxf(m[g], s);
-            const float corr = expf(m[g] - m_new);          // exp(-inf) = 0 on the first key
-            const float pe = expf(s - m_new);
-            l[g] = l[g] * corr + pe;
+        }
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) acc[g][j] = acc[g][j] * corr + pe * kr[j];
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int g = 0; g < LAT_HG; ++g) {
+#pragma unroll
+                for (int b = 0; b < KB; ++b) sc[g][b] += __shfl_xor_sync(0xffffffffu, sc[g][b], o);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < LAT_HG; ++g) {
+            float m_new = m[g];
+#pragma unroll
+            for (int b = 0; b < KB; ++b) {
+                sc[g][b] *= scale;
+                if (p0 + b < hi) m_new = fmaxf(m_new, sc[g][b]);
+            }
+            const float corr = expf(m[g] - m_new);          // exp(-inf) = 0 on the first keys
+            l[g] *= corr;
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) acc[g][j] *= corr;
+#pragma unroll
+            for (int b = 0; b < KB; ++b) {
+                const float pe = p0 + b < hi ? expf(sc[g][b] - m_new) : 0.f;
+                l[g] += pe;
+#pragma unroll
+                for (int j = 0; j < EPL; ++j) acc[g][j] += pe * kr[b][j];
+            }
             m[g] = m_new;
         }
     }

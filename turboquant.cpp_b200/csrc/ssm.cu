@@ -9,7 +9,7 @@
 // Everything here is fp32: the projection arrives as fp32, decays, step sizes and the state never leave it.
 //   conv_silu          the convolution over the step's tokens, reading the kept inputs for a run's first tokens
 //   conv_state_update  the kept inputs after the step (a launch of its own: conv_silu reads the old ones)
-//   ssm_scan           the recurrence over each sequence's run of new tokens, state in registers
+//   ssm_scan           the recurrence over each sequence's run of new tokens, a warp per column of the state
 //   gated_group_norm   y * silu(z), RMS norm in equal groups, weight
 #include "common.cuh"
 
@@ -17,8 +17,6 @@ TQ_DEFINE_LAST_ERROR
 
 #define SSM_MAX_TAPS 8
 #define SSM_MAX_STATE 256
-#define SSM_NPT 32            // rows of the state a thread keeps
-#define SSM_VT 32             // columns of the state per block (a warp's lanes)
 
 template <typename TW>
 __global__ void conv_silu_kernel(const float* __restrict__ proj, int P, int off, const TW* __restrict__ w,
@@ -85,51 +83,58 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
 }
 
 // ---------------------------------------------------------------------------------------
-// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_VT)), block (SSM_VT, NS): thread (v, part) keeps rows
-// part*SSM_NPT .. of column v of the state in registers for the whole run.  The run is walked in chunks of TC
-// steps: the chunk's B, C, x, step sizes and decays are staged in shared memory, every thread advances its rows
-// through the chunk and leaves its share of each step's y, and the shares are added in part order.
+// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_COLS warps per block.  A warp owns one column v of
+// the head's state: lane l keeps rows l, l+32, ... (RPL of them) in registers for the whole run, so a step is RPL
+// multiply-adds for the state, RPL for y and one sum over the warp's lanes, with no barrier between steps.  The run
+// is walked in chunks of TC steps whose B, C, x, step sizes and decays are staged in shared memory (rows beyond N
+// are staged as zeros, so the state's padding rows stay zero and need no test).
 // ---------------------------------------------------------------------------------------
-template <typename TW>
-__global__ void ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
-                                const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
-                                float* __restrict__ state, long long slot_stride, float* __restrict__ y,
-                                int heads, int vdim, int N, int groups, int TC, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots) {
+#define SSM_COLS 16
+
+template <typename TW, int RPL>
+__global__ void __launch_bounds__(32 * SSM_COLS)
+ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
+                const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
+                float* __restrict__ state, long long slot_stride, float* __restrict__ y, int heads, int vdim, int N,
+                int groups, int TC, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     extern __shared__ float ssm_smem[];
-    const int NS = blockDim.y;
-    float* Bs = ssm_smem;                    // [TC][N]
-    float* Cs = Bs + TC * N;                 // [TC][N]
-    float* xs = Cs + TC * N;                 // [TC][SSM_VT]
-    float* yp = xs + TC * SSM_VT;            // [TC][NS][SSM_VT]
-    float* dts = yp + TC * NS * SSM_VT;      // [TC]
+    constexpr int NP = 32 * RPL;             // rows with padding
+    float* Bs = ssm_smem;                    // [TC][NP]
+    float* Cs = Bs + TC * NP;                // [TC][NP]
+    float* xs = Cs + TC * NP;                // [TC][SSM_COLS]
+    float* dts = xs + TC * SSM_COLS;         // [TC]
     float* dec = dts + TC;                   // [TC]
-    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * SSM_VT;
-    const int lane = threadIdx.x, part = threadIdx.y, tid = part * SSM_VT + lane, nthreads = NS * SSM_VT;
-    const int v = v0 + lane;
+    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * SSM_COLS;
+    const int tid = threadIdx.x, lane = tid & 31, col = tid >> 5, nthreads = 32 * SSM_COLS;
+    const int v = v0 + col;
     const int g = h / (heads / groups);
     const int inner = heads * vdim;
     const int first = cu_seqlens[s], n = cu_seqlens[s + 1] - first;
     const float A = -expf(tq_to_float(a_log[h])), bias = tq_to_float(dt_bias[h]), D = tq_to_float(d_skip[h]);
     float* Sg = state + (size_t)slots[s] * slot_stride + ((size_t)h * N) * vdim;
-    float S[SSM_NPT];
+    float S[RPL];
 #pragma unroll
-    for (int r = 0; r < SSM_NPT; ++r) {
-        const int row = part * SSM_NPT + r;
+    for (int r = 0; r < RPL; ++r) {
+        const int row = lane + 32 * r;
         S[r] = (row < N && v < vdim) ? Sg[(size_t)row * vdim + v] : 0.f;
     }
     for (int t0 = 0; t0 < n; t0 += TC) {
         const int tc = min(TC, n - t0);
-        for (int k = tid; k < tc * N; k += nthreads) {
-            const int tt = k / N, r = k % N;
-            const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + (size_t)g * N + r;
-            Bs[tt * N + r] = row[0];
-            Cs[tt * N + r] = row[(size_t)groups * N];
+        for (int k = tid; k < tc * NP; k += nthreads) {
+            const int tt = k / NP, r = k % NP;
+            float bv = 0.f, cv = 0.f;
+            if (r < N) {
+                const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + (size_t)g * N + r;
+                bv = row[0];
+                cv = row[(size_t)groups * N];
+            }
+            Bs[k] = bv;
+            Cs[k] = cv;
         }
-        for (int k = tid; k < tc * SSM_VT; k += nthreads) {
-            const int tt = k / SSM_VT, vv = v0 + k % SSM_VT;
+        for (int k = tid; k < tc * SSM_COLS; k += nthreads) {
+            const int tt = k / SSM_COLS, vv = v0 + k % SSM_COLS;
             xs[k] = vv < vdim ? xbc[(size_t)(first + t0 + tt) * C + (size_t)h * vdim + vv] : 0.f;
         }
         if (tid < tc) {
@@ -139,34 +144,33 @@ __global__ void ssm_scan_kernel(const float* __restrict__ xbc, int C, const floa
             dec[tid] = expf(A * dt);
         }
         __syncthreads();
+#pragma unroll 4
         for (int tt = 0; tt < tc; ++tt) {
-            const float a = dec[tt], dtx = dts[tt] * xs[tt * SSM_VT + lane];
-            const float* Bt = Bs + tt * N + part * SSM_NPT;
-            const float* Ct = Cs + tt * N + part * SSM_NPT;
+            const float xv = xs[tt * SSM_COLS + col];
+            const float a = dec[tt], dtx = dts[tt] * xv;
             float acc = 0.f;
 #pragma unroll
-            for (int r = 0; r < SSM_NPT; ++r) {
-                if (part * SSM_NPT + r < N) {
-                    S[r] = a * S[r] + dtx * Bt[r];
-                    acc += S[r] * Ct[r];
-                }
+            for (int r = 0; r < RPL; ++r) {
+                S[r] = a * S[r] + dtx * Bs[tt * NP + lane + 32 * r];
+                acc += S[r] * Cs[tt * NP + lane + 32 * r];
             }
-            yp[(tt * NS + part) * SSM_VT + lane] = acc;
-        }
-        __syncthreads();
-        for (int tt = part; tt < tc; tt += NS) {
-            float acc = 0.f;
-            for (int p = 0; p < NS; ++p) acc += yp[(tt * NS + p) * SSM_VT + lane];
-            if (v < vdim) y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + v] = acc + D * xs[tt * SSM_VT + lane];
+            acc = tq_warp_sum(acc);
+            if (lane == 0 && v < vdim) y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + v] = acc + D * xv;
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < SSM_NPT; ++r) {
-        const int row = part * SSM_NPT + r;
+    for (int r = 0; r < RPL; ++r) {
+        const int row = lane + 32 * r;
         if (row < N && v < vdim) Sg[(size_t)row * vdim + v] = S[r];
     }
 }
+
+#define SSM_LAUNCH(RPL_)                                                                                          \
+    TQ_DISPATCH(w_dtype, TW,                                                                                      \
+        (tq_launch(grid, 32 * SSM_COLS, smem, stream)(ssm_scan_kernel<TW, RPL_>, xbc, C, proj, P, dt_off,         \
+            (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, TC, \
+            cu_seqlens, slots)))
 
 TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
                           const void* a_log, const void* d_skip, int w_dtype, float* state, long long slot_stride,
@@ -177,15 +181,16 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
     TQ_REQUIRE(N >= 1 && N <= SSM_MAX_STATE, "ssm_scan: state size %d (1..%d)", N, SSM_MAX_STATE);
     TQ_REQUIRE(C == heads * vdim + 2 * groups * N, "ssm_scan: %d channels for %d heads x %d and %d groups x %d", C, heads, vdim, groups, N);
     TQ_REQUIRE(dt_off >= 0 && dt_off + heads <= P, "ssm_scan: the step sizes lie outside the projection");
-    const int NS = (N + SSM_NPT - 1) / SSM_NPT;
-    const int TC = N > 128 ? 8 : 16;
-    dim3 grid(n_seqs, heads, (vdim + SSM_VT - 1) / SSM_VT), block(SSM_VT, NS);
+    const int RPL = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 128 ? 4 : 8));
+    const int NP = 32 * RPL;
+    const int TC = NP <= 128 ? 32 : 16;
+    dim3 grid(n_seqs, heads, (vdim + SSM_COLS - 1) / SSM_COLS);
     TQ_REQUIRE(heads <= 65535 && grid.z <= 65535, "ssm_scan: sizes exceed the grid limit");
-    const size_t smem = (size_t)(2 * TC * N + TC * SSM_VT + TC * NS * SSM_VT + 2 * TC) * sizeof(float);
-    TQ_DISPATCH(w_dtype, TW,
-        (tq_launch(grid, block, smem, stream)(ssm_scan_kernel<TW>, xbc, C, proj, P, dt_off, (const TW*)dt_bias,
-                                              (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N,
-                                              groups, TC, cu_seqlens, slots)));
+    const size_t smem = (size_t)(2 * TC * NP + TC * SSM_COLS + 2 * TC) * sizeof(float);
+    if (RPL == 1) SSM_LAUNCH(1);
+    else if (RPL == 2) SSM_LAUNCH(2);
+    else if (RPL == 4) SSM_LAUNCH(4);
+    else SSM_LAUNCH(8);
     TQ_CHECK_LAUNCH("ssm_scan");
     return 0;
 }

@@ -40,14 +40,13 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], norm_weight: Op
 
 
 def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:
-    """Key ranges per token so that a step of few tokens still fills the GPU: none for prompts, up to 32 for
-    single tokens over long ranges.  The ranges are joined in range order, so a launch shape gives the same bits
-    every time; logits agree across shapes to rounding."""
+    """Key ranges per token.  A block walks its range four keys at a time (one per warp), so a step of few tokens
+    over long ranges is cut until a block has about 32 keys or the launch has eight waves of blocks; prompts
+    (many tokens) are not cut.  The ranges are joined in range order, so a launch shape gives the same bits every
+    time; logits agree across shapes to rounding."""
     blocks = n_tokens * -(-heads // HEADS_PER_BLOCK)
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    if blocks >= 2 * sms or longest < 256:
-        return 1
-    return int(max(1, min(32, (2 * sms) // blocks, longest // 128)))
+    return int(max(1, min(64, longest // 32, (8 * sms) // blocks)))
 
 
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: torch.Tensor, sink: Optional[torch.Tensor],
@@ -78,7 +77,7 @@ def latent_gather(cache: torch.Tensor, table_row: torch.Tensor, page_size: int, 
     """out[j] = the cached row of position k0 + j of the sequence whose pages table_row lists, j < n."""
     want_int32(table_row, "the page table")
     Dk = cache.shape[-1]
-    if out.shape != (n, Dk) or out.dtype != cache.dtype:
+    if tuple(out.shape) != (n, Dk) or out.dtype != cache.dtype:
         raise KernelError("latent_gather: the output must be [n, row] in the cache's dtype")
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_latent_gather(ptr(cache), c_int(code(cache.dtype)), ptr(table_row), c_int(table_row.shape[0]),

@@ -123,7 +123,7 @@ class LatentAttentionMixer(Mixer):
         the step only, so it runs inside the decode graphs."""
         T, H, R = q_lat.shape
         longest = min(self.window, ctx.max_kv_len) if self.window else ctx.max_kv_len
-        n_splits = KL.splits_for(T, H, longest, xn.device)
+        n_splits = KL.splits_for(T, H, longest, q.device)
         partial = torch.empty(T * H * n_splits * (R + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
         KL.latent_attention(q_lat, q, self.dim, cache.kv, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                             cache.page_size, self.window, self.scale, sums, H, R, self.rot_dim, n_splits, partial)
@@ -143,8 +143,14 @@ class LatentAttentionMixer(Mixer):
                 b = min(n, a + block)
                 pos0, k1 = start + a, start + b
                 k0 = max(0, pos0 + 1 - self.window) if self.window else 0
-                rows = torch.empty((k1 - k0, Dk), dtype=act, device=dev)
-                KL.latent_gather(cache.kv, cache.page_table[i], cache.page_size, k0, k1 - k0, rows)
+                # the library's fast products want dimensions that are multiples of 64 elements: the block's rows are
+                # padded with zero rows, which the softmax gives weight 0 (they lie behind the block's last position)
+                n_keys = k1 - k0
+                n_pad = -(-n_keys // 64) * 64
+                rows = torch.empty((n_pad, Dk), dtype=act, device=dev)
+                KL.latent_gather(cache.kv, cache.page_table[i], cache.page_size, k0, n_keys, rows[:n_keys])
+                if n_pad > n_keys:
+                    rows[n_keys:].zero_()
                 qa = torch.empty((b - a, H, Dk), dtype=act, device=dev)            # [query in the latent space | rotated part]
                 qa[:, :, :R].copy_(q_lat[t0 + a:t0 + b])
                 if self.rot_dim:
