@@ -76,7 +76,7 @@ def test_latent_attention_with_one_key_that_stands_out(dtype, H, R, rot, window,
         ref = plain_rows_attention(ql[0].float().cpu().numpy().astype(np.float64),
                                    qfull.view(H, 5 + rot)[:, 5:].float().cpu().numpy().astype(np.float64), rows, R, sink,
                                    window, scale, p)
-        for n_splits in (1, 3):
+        for n_splits in (1, 3, 7):
             out = torch.empty((1, H, R), dtype=dtype, device=DEV)
             partial = torch.empty(H * n_splits * (R + 2), dtype=torch.float32, device=DEV)
             KL.latent_attention(ql, qfull, 5, cache, dev(sink), i32([p]), i32([0]), table, page_size, window, scale, out, H,

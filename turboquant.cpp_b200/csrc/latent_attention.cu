@@ -139,12 +139,22 @@ latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, 
     float* s_acc = lat_smem + LAT_HG * Dk;      // [LAT_WARPS][R]
     const int t = blockIdx.x, h0 = blockIdx.y * LAT_HG;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int k = threadIdx.x; k < LAT_HG * Dk; k += blockDim.x) {
-        const int g = k / Dk, e = k % Dk, h = h0 + g;
-        float v = 0.f;
-        if (h < H) v = e < R ? tq_to_float(q_lat[((size_t)t * H + h) * R + e])
-                             : tq_to_float(q[((size_t)t * H + h) * q_dim + q_off + (e - R)]);
-        qs[k] = v;
+    {   // the heads' queries: every thread's loads are issued together (at most EPL of them), then stored
+        float tmp[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int k = threadIdx.x + i * LAT_WARPS * 32;
+            const int g = k / Dk, e = k - g * Dk, h = h0 + g;
+            tmp[i] = 0.f;
+            if (k < LAT_HG * Dk && h < H)
+                tmp[i] = e < R ? tq_to_float(q_lat[((size_t)t * H + h) * R + e])
+                               : tq_to_float(q[((size_t)t * H + h) * q_dim + q_off + (e - R)]);
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int k = threadIdx.x + i * LAT_WARPS * 32;
+            if (k < LAT_HG * Dk) qs[k] = tmp[i];
+        }
     }
     __syncthreads();
     const int pos = positions[t];
@@ -282,6 +292,169 @@ latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, 
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same on tensor cores (bfloat16, R a multiple of 32 up to 512, R + rot a multiple of 16): the block's sixteen
+// heads are the sixteen rows of mma.sync m16n8k16, so one cached row serves sixteen dot products per
+// instruction.  Keys come in tiles of sixteen through shared memory.  Every warp computes the tile's scores
+// (16 heads x 16 keys, fp32 accumulators; scale, mask and the online softmax on the accumulator fragments) and
+// owns a quarter of the R output columns, for which it multiplies the weights (rounded to bfloat16, as the
+// second operand's type demands) with the tile's rows; computing the scores four times over costs less than
+// passing them between warps, and leaves no barrier inside a tile.
+// ---------------------------------------------------------------------------------------
+#define LATM_HEADS 16
+#define LATM_KEYS 16
+#define LATM_PAD 8            // bfloat16 elements between rows in shared memory: fragment reads hit 32 different banks
+
+__device__ __forceinline__ void lat_mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lat_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int OT>      // output n-tiles (of 8 columns) per warp: R = 32 * OT
+__global__ void __launch_bounds__(LAT_WARPS * 32)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q, int q_dim,
+                            int q_off, const __nv_bfloat16* __restrict__ cache, const float* __restrict__ sink,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ page_table, int table_stride, int page_size, int window, float scale,
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int R, int rot,
+                            int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    extern __shared__ uint4 latm_smem[];
+    const int Dk = R + rot, ld = Dk + LATM_PAD;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(latm_smem);       // [16 heads][ld]
+    __nv_bfloat16* Ks = Qs + LATM_HEADS * ld;                               // [16 keys][ld]
+    const int t = blockIdx.x, h0 = blockIdx.y * LATM_HEADS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tq = lane & 3;
+    for (int k = threadIdx.x; k < LATM_HEADS * Dk; k += blockDim.x) {
+        const int r = k / Dk, e = k - r * Dk, h = h0 + r;
+        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+        if (h < H) v = e < R ? q_lat[((size_t)t * H + h) * R + e] : q[((size_t)t * H + h) * q_dim + q_off + (e - R)];
+        Qs[r * ld + e] = v;
+    }
+    const int pos = positions[t];
+    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int n_keys = pos + 1 - first;
+    const int per = (n_keys + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int lo = first + (int)blockIdx.z * per, hi = min(pos + 1, lo + per);
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+    const int chunks = Dk / 8;                                              // 16-byte pieces of a row
+
+    float o[OT][4];
+#pragma unroll
+    for (int j = 0; j < OT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};                 // rows g and g + 8
+    const int col_base = warp * OT * 8;
+
+    for (int p0 = lo; p0 < hi; p0 += LATM_KEYS) {
+        __syncthreads();                                                    // the tile before has been used (and Qs is written)
+        for (int k = threadIdx.x; k < LATM_KEYS * chunks; k += blockDim.x) {
+            const int r = k / chunks, c = k - r * chunks, p = p0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (p < hi) {
+                const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+                v = reinterpret_cast<const uint4*>(cache + ((size_t)page * page_size + p % page_size) * Dk)[c];
+            }
+            *reinterpret_cast<uint4*>(Ks + r * ld + 8 * c) = v;
+        }
+        __syncthreads();
+        // scores: 16 heads x 16 keys
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        for (int k0 = 0; k0 < Dk; k0 += 16) {
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * ld + k0 + 2 * tq);
+            a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * ld + k0 + 2 * tq);
+            a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * ld + k0 + 2 * tq + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * ld + k0 + 2 * tq + 8);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const __nv_bfloat16* kp = Ks + (nt * 8 + g) * ld + k0 + 2 * tq;
+                lat_mma16816(sc[nt], a, *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            }
+        }
+        // scale, mask, online softmax: this lane holds keys nt*8 + 2*tq + {0,1} of rows g (values 0,1) and g+8 (values 2,3)
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const bool seen = p0 + nt * 8 + 2 * tq + (i & 1) < hi;
+                sc[nt][i] = seen ? sc[nt][i] * scale : -INFINITY;
+                tmax[i >> 1] = fmaxf(tmax[i >> 1], sc[nt][i]);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+            const float m_new = fmaxf(m[r], tmax[r]);          // finite: a tile has at least one key
+            corr[r] = expf(m[r] - m_new);                       // exp(-inf) = 0 on the first tile
+            m[r] = m_new;
+            l[r] *= corr[r];
+        }
+        uint32_t pa[4];
+        {
+            float pe[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    pe[nt][i] = expf(sc[nt][i] - m[i >> 1]);
+                    l[i >> 1] += pe[nt][i];                     // this lane's share; the quad's shares are added at the end
+                }
+            }
+            pa[0] = lat_pack(pe[0][0], pe[0][1]);
+            pa[1] = lat_pack(pe[0][2], pe[0][3]);
+            pa[2] = lat_pack(pe[1][0], pe[1][1]);
+            pa[3] = lat_pack(pe[1][2], pe[1][3]);
+        }
+        const unsigned short* Ku = reinterpret_cast<const unsigned short*>(Ks);
+#pragma unroll
+        for (int j = 0; j < OT; ++j) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            const int col = col_base + j * 8 + g;
+            const uint32_t b0 = (uint32_t)Ku[(2 * tq) * ld + col] | ((uint32_t)Ku[(2 * tq + 1) * ld + col] << 16);
+            const uint32_t b1 = (uint32_t)Ku[(2 * tq + 8) * ld + col] | ((uint32_t)Ku[(2 * tq + 9) * ld + col] << 16);
+            lat_mma16816(o[j], pa, b0, b1);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    const bool whole = gridDim.z == 1;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int h = h0 + g + 8 * r;
+        if (h >= H) continue;
+        if (whole) {
+            const float sk = sink ? sink[h] : -INFINITY;
+            const float M = fmaxf(m[r], sk);
+            const float f = m[r] == -INFINITY ? 0.f : expf(m[r] - M);
+            const float inv = 1.0f / (l[r] * f + (sink ? expf(sk - M) : 0.f));
+            __nv_bfloat16* op = out + ((size_t)t * H + h) * R + col_base + 2 * tq;
+#pragma unroll
+            for (int j = 0; j < OT; ++j)
+                *reinterpret_cast<__nv_bfloat162*>(op + j * 8) = __floats2bfloat162_rn(o[j][2 * r] * f * inv, o[j][2 * r + 1] * f * inv);
+        } else {
+            float* pp = partial + (((size_t)t * H + h) * gridDim.z + blockIdx.z) * (R + 2);
+            if (warp == 0 && tq == 0) { pp[0] = m[r]; pp[1] = l[r]; }       // an empty range leaves -inf and 0
+#pragma unroll
+            for (int j = 0; j < OT; ++j) {
+                pp[2 + col_base + j * 8 + 2 * tq] = o[j][2 * r];
+                pp[2 + col_base + j * 8 + 2 * tq + 1] = o[j][2 * r + 1];
+            }
+        }
+    }
+}
+
 // joins the ranges of one (token, head) in range order and lets the sink take part
 template <typename TA>
 __global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, int n_splits,
@@ -308,6 +481,12 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, const flo
     }
 }
 
+// TQ_LATENT_NO_MMA=1: the CUDA-core form for bfloat16 too
+static bool lat_use_mma() {
+    static const bool on = [] { const char* e = getenv("TQ_LATENT_NO_MMA"); return !(e && e[0] && e[0] != '0'); }();
+    return on;
+}
+
 #define LAT_LAUNCH(TA, EPL, VEC)                                                                                  \
     tq_launch(grid, LAT_WARPS * 32, smem, stream)(latent_attention_kernel<TA, EPL, VEC>, (const TA*)q_lat,        \
         (const TA*)q, q_dim, q_off, (const TA*)cache, sink, positions, seq_of_token, page_table, table_stride,    \
@@ -327,6 +506,23 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
                "scratch buffer", n_splits);
     TQ_REQUIRE((H + LAT_HG - 1) / LAT_HG <= 65535, "latent_attention: %d heads exceed the grid limit", H);
     TQ_REQUIRE(rot == 0 || (q && q_off >= 0 && q_off + rot <= q_dim), "latent_attention: the queries' rotated part does not fit");
+    const bool mma = act_dtype == TQ_BF16 && Dk % 16 == 0 && R % 32 == 0 && R <= 512 && (q_dim % 2 == 0) &&
+                     ((uintptr_t)cache % 16) == 0 && ((uintptr_t)out % 4) == 0 && lat_use_mma();
+    if (mma) {
+        dim3 grid(T_, (H + LATM_HEADS - 1) / LATM_HEADS, n_splits);
+        TQ_REQUIRE(grid.y <= 65535, "latent_attention: %d heads exceed the grid limit", H);
+        const size_t smem = (size_t)(LATM_HEADS + LATM_KEYS) * (Dk + LATM_PAD) * sizeof(__nv_bfloat16);
+#define LATM_LAUNCH(OT_)                                                                                           \
+        tq_launch(grid, LAT_WARPS * 32, smem, stream)(latent_attention_mma_kernel<OT_>, (const __nv_bfloat16*)q_lat,   \
+            (const __nv_bfloat16*)q, q_dim, q_off, (const __nv_bfloat16*)cache, sink, positions, seq_of_token, page_table, \
+            table_stride, page_size, window, scale, (__nv_bfloat16*)out, partial, H, R, rot, n_seqs, n_pages)
+        const int OT = R / 32;
+        if (OT <= 2) { if (OT == 1) LATM_LAUNCH(1); else LATM_LAUNCH(2); }
+        else if (OT <= 4) { if (OT == 3) LATM_LAUNCH(3); else LATM_LAUNCH(4); }
+        else if (OT <= 8) { if (OT <= 6) { if (OT == 5) LATM_LAUNCH(5); else LATM_LAUNCH(6); } else { if (OT == 7) LATM_LAUNCH(7); else LATM_LAUNCH(8); } }
+        else if (OT <= 12) { if (OT <= 10) { if (OT == 9) LATM_LAUNCH(9); else LATM_LAUNCH(10); } else { if (OT == 11) LATM_LAUNCH(11); else LATM_LAUNCH(12); } }
+        else { if (OT <= 14) { if (OT == 13) LATM_LAUNCH(13); else LATM_LAUNCH(14); } else { if (OT == 15) LATM_LAUNCH(15); else LATM_LAUNCH(16); } }
+    } else {
     dim3 grid(T_, (H + LAT_HG - 1) / LAT_HG, n_splits);
     const size_t smem = (size_t)(LAT_HG * Dk + LAT_WARPS * R) * sizeof(float);
     const bool vec = Dk % 4 == 0 && R % 4 == 0 && ((uintptr_t)cache % 16) == 0;
@@ -337,6 +533,7 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
         else if (Dk <= 640) LAT_LAUNCH(TA, 20, 4);
         else LAT_LAUNCH(TA, 32, 4);
     });
+    }
     TQ_CHECK_LAUNCH("latent_attention");
     if (n_splits > 1) {
         dim3 mgrid(T_, H);

@@ -9,7 +9,7 @@
 // Everything here is fp32: the projection arrives as fp32, decays, step sizes and the state never leave it.
 //   conv_silu          the convolution over the step's tokens, reading the kept inputs for a run's first tokens
 //   conv_state_update  the kept inputs after the step (a launch of its own: conv_silu reads the old ones)
-//   ssm_scan           the recurrence over each sequence's run of new tokens, a warp per column of the state
+//   ssm_scan           the recurrence over each sequence's run of new tokens, a warp per four columns of the state
 //   gated_group_norm   y * silu(z), RMS norm in equal groups, weight
 #include "common.cuh"
 
@@ -83,93 +83,139 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
 }
 
 // ---------------------------------------------------------------------------------------
-// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_COLS warps per block.  A warp owns one column v of
-// the head's state: lane l keeps rows l, l+32, ... (RPL of them) in registers for the whole run, so a step is RPL
-// multiply-adds for the state, RPL for y and one sum over the warp's lanes, with no barrier between steps.  The run
-// is walked in chunks of TC steps whose B, C, x, step sizes and decays are staged in shared memory (rows beyond N
-// are staged as zeros, so the state's padding rows stay zero and need no test).
+// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_WARPS warps per block.  A warp owns SSM_CPW
+// neighbouring columns of the head's state: lane l keeps rows l, l+32, ... (RPL of them) of each column in
+// registers for the whole run, so a step reads its B and C values once for the four columns, does RPL x 4
+// multiply-adds for the state and as many for y, and sums the four y over the warp's lanes with six shuffles
+// (the lanes halve the set of columns they carry twice, then add up within groups of eight).  No barrier
+// between steps.  The run is walked in chunks of TC steps whose B, C, x, step sizes and decays lie in shared
+// memory (rows beyond N as zeros, so the state's padding rows stay zero and need no test); a chunk's inputs are
+// fetched into registers, all loads in flight together, while the chunk before is being computed.
 // ---------------------------------------------------------------------------------------
-#define SSM_COLS 16
+#define SSM_WARPS 8
+#define SSM_CPW 4
+#define SSM_COLS (SSM_WARPS * SSM_CPW)
 
-template <typename TW, int RPL>
-__global__ void __launch_bounds__(32 * SSM_COLS)
+template <typename TW, int RPL, int TC>
+__global__ void __launch_bounds__(32 * SSM_WARPS)
 ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, float* __restrict__ y, int heads, int vdim, int N,
-                int groups, int TC, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
+                int groups, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    extern __shared__ float ssm_smem[];
+    extern __shared__ float4 ssm_smem4[];
+    float* ssm_smem = reinterpret_cast<float*>(ssm_smem4);
     constexpr int NP = 32 * RPL;             // rows with padding
-    float* Bs = ssm_smem;                    // [TC][NP]
+    constexpr int NT = 32 * SSM_WARPS;
+    float* xs = ssm_smem;                    // [TC][SSM_COLS]  (first: 16-byte reads)
+    float* Bs = xs + TC * SSM_COLS;          // [TC][NP]
     float* Cs = Bs + TC * NP;                // [TC][NP]
-    float* xs = Cs + TC * NP;                // [TC][SSM_COLS]
-    float* dts = xs + TC * SSM_COLS;         // [TC]
+    float* dts = Cs + TC * NP;               // [TC]
     float* dec = dts + TC;                   // [TC]
     const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * SSM_COLS;
-    const int tid = threadIdx.x, lane = tid & 31, col = tid >> 5, nthreads = 32 * SSM_COLS;
-    const int v = v0 + col;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int vw = v0 + warp * SSM_CPW;      // the warp's first column
     const int g = h / (heads / groups);
     const int inner = heads * vdim;
     const int first = cu_seqlens[s], n = cu_seqlens[s + 1] - first;
     const float A = -expf(tq_to_float(a_log[h])), bias = tq_to_float(dt_bias[h]), D = tq_to_float(d_skip[h]);
     float* Sg = state + (size_t)slots[s] * slot_stride + ((size_t)h * N) * vdim;
-    float S[RPL];
+    float S[RPL][SSM_CPW];
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
-        const int row = lane + 32 * r;
-        S[r] = (row < N && v < vdim) ? Sg[(size_t)row * vdim + v] : 0.f;
+#pragma unroll
+        for (int c = 0; c < SSM_CPW; ++c) {
+            const int row = lane + 32 * r;
+            S[r][c] = (row < N && vw + c < vdim) ? Sg[(size_t)row * vdim + vw + c] : 0.f;
+        }
     }
+    constexpr int LPT = TC * NP / NT;                    // B and C values per thread and chunk
+    constexpr int XPT = TC * SSM_COLS / NT;              // x values per thread and chunk
+    float pb[LPT], pc[LPT], px[XPT], praw = 0.f;
+    auto fetch = [&](int t0) {
+        const int tc = min(TC, n - t0);
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+            const int k = tid + i * NT, tt = k / NP, r = k % NP;
+            pb[i] = pc[i] = 0.f;
+            if (tt < tc && r < N) {
+                const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + (size_t)g * N + r;
+                pb[i] = row[0];
+                pc[i] = row[(size_t)groups * N];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < XPT; ++i) {
+            const int k = tid + i * NT, tt = k / SSM_COLS, vv = v0 + k % SSM_COLS;
+            px[i] = (tt < tc && vv < vdim) ? xbc[(size_t)(first + t0 + tt) * C + (size_t)h * vdim + vv] : 0.f;
+        }
+        if (tid < tc) praw = proj[(size_t)(first + t0 + tid) * P + dt_off + h];
+    };
+    if (n > 0) fetch(0);
+    const bool hi16 = lane & 16, hi8 = lane & 8;
+    const int my_col = (hi16 ? 2 : 0) + (hi8 ? 1 : 0);   // the column whose sum this lane ends up with
     for (int t0 = 0; t0 < n; t0 += TC) {
         const int tc = min(TC, n - t0);
-        for (int k = tid; k < tc * NP; k += nthreads) {
-            const int tt = k / NP, r = k % NP;
-            float bv = 0.f, cv = 0.f;
-            if (r < N) {
-                const float* row = xbc + (size_t)(first + t0 + tt) * C + inner + (size_t)g * N + r;
-                bv = row[0];
-                cv = row[(size_t)groups * N];
-            }
-            Bs[k] = bv;
-            Cs[k] = cv;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+            Bs[tid + i * NT] = pb[i];
+            Cs[tid + i * NT] = pc[i];
         }
-        for (int k = tid; k < tc * SSM_COLS; k += nthreads) {
-            const int tt = k / SSM_COLS, vv = v0 + k % SSM_COLS;
-            xs[k] = vv < vdim ? xbc[(size_t)(first + t0 + tt) * C + (size_t)h * vdim + vv] : 0.f;
-        }
+#pragma unroll
+        for (int i = 0; i < XPT; ++i) xs[tid + i * NT] = px[i];
         if (tid < tc) {
-            const float raw = proj[(size_t)(first + t0 + tid) * P + dt_off + h] + bias;
+            const float raw = praw + bias;
             const float dt = raw > 20.f ? raw : log1pf(expf(raw));
             dts[tid] = dt;
             dec[tid] = expf(A * dt);
         }
         __syncthreads();
-#pragma unroll 4
+        if (t0 + TC < n) fetch(t0 + TC);
+#pragma unroll 2
         for (int tt = 0; tt < tc; ++tt) {
-            const float xv = xs[tt * SSM_COLS + col];
-            const float a = dec[tt], dtx = dts[tt] * xv;
-            float acc = 0.f;
+            const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * SSM_COLS + warp * SSM_CPW);
+            const float xv[SSM_CPW] = {x4.x, x4.y, x4.z, x4.w};
+            const float a = dec[tt], dt = dts[tt];
+            float acc[SSM_CPW] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < RPL; ++r) {
-                S[r] = a * S[r] + dtx * Bs[tt * NP + lane + 32 * r];
-                acc += S[r] * Cs[tt * NP + lane + 32 * r];
+                const float bv = Bs[tt * NP + lane + 32 * r] * dt, cv = Cs[tt * NP + lane + 32 * r];
+#pragma unroll
+                for (int c = 0; c < SSM_CPW; ++c) {
+                    S[r][c] = a * S[r][c] + bv * xv[c];
+                    acc[c] += S[r][c] * cv;
+                }
             }
-            acc = tq_warp_sum(acc);
-            if (lane == 0 && v < vdim) y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + v] = acc + D * xv;
+            // lanes with bit 4 clear go on with columns 0 and 1, the others with 2 and 3; then bit 3 picks one
+            float k0 = hi16 ? acc[2] : acc[0], k1 = hi16 ? acc[3] : acc[1];
+            k0 += __shfl_xor_sync(0xffffffffu, hi16 ? acc[0] : acc[2], 16);
+            k1 += __shfl_xor_sync(0xffffffffu, hi16 ? acc[1] : acc[3], 16);
+            float k = hi8 ? k1 : k0;
+            k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+            k += __shfl_xor_sync(0xffffffffu, k, 4);
+            k += __shfl_xor_sync(0xffffffffu, k, 2);
+            k += __shfl_xor_sync(0xffffffffu, k, 1);
+            const float xm = hi16 ? (hi8 ? xv[3] : xv[2]) : (hi8 ? xv[1] : xv[0]);
+            if ((lane & 7) == 0 && vw + my_col < vdim)
+                y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + vw + my_col] = k + D * xm;
         }
         __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
-        const int row = lane + 32 * r;
-        if (row < N && v < vdim) Sg[(size_t)row * vdim + v] = S[r];
+#pragma unroll
+        for (int c = 0; c < SSM_CPW; ++c) {
+            const int row = lane + 32 * r;
+            if (row < N && vw + c < vdim) Sg[(size_t)row * vdim + vw + c] = S[r][c];
+        }
     }
 }
 
-#define SSM_LAUNCH(RPL_)                                                                                          \
+#define SSM_LAUNCH(RPL_, TC_)                                                                                     \
     TQ_DISPATCH(w_dtype, TW,                                                                                      \
-        (tq_launch(grid, 32 * SSM_COLS, smem, stream)(ssm_scan_kernel<TW, RPL_>, xbc, C, proj, P, dt_off,         \
-            (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, TC, \
+        (tq_launch(grid, 32 * SSM_WARPS, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_>, xbc, C, proj, P, dt_off,    \
+            (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, \
             cu_seqlens, slots)))
 
 TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
@@ -187,10 +233,10 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
     dim3 grid(n_seqs, heads, (vdim + SSM_COLS - 1) / SSM_COLS);
     TQ_REQUIRE(heads <= 65535 && grid.z <= 65535, "ssm_scan: sizes exceed the grid limit");
     const size_t smem = (size_t)(2 * TC * NP + TC * SSM_COLS + 2 * TC) * sizeof(float);
-    if (RPL == 1) SSM_LAUNCH(1);
-    else if (RPL == 2) SSM_LAUNCH(2);
-    else if (RPL == 4) SSM_LAUNCH(4);
-    else SSM_LAUNCH(8);
+    if (RPL == 1) SSM_LAUNCH(1, 32);
+    else if (RPL == 2) SSM_LAUNCH(2, 32);
+    else if (RPL == 4) SSM_LAUNCH(4, 32);
+    else SSM_LAUNCH(8, 16);
     TQ_CHECK_LAUNCH("ssm_scan");
     return 0;
 }

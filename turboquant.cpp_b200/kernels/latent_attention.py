@@ -39,14 +39,23 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], norm_weight: Op
         c_int(cache.shape[0] if cache is not None else 0), stream()))
 
 
-def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:
-    """Key ranges per token.  A block walks its range four keys at a time (one per warp), so a step of few tokens
-    over long ranges is cut until a block has about 32 keys or the launch has eight waves of blocks; prompts
-    (many tokens) are not cut.  The ranges are joined in range order, so a launch shape gives the same bits every
-    time; logits agree across shapes to rounding."""
-    blocks = n_tokens * -(-heads // HEADS_PER_BLOCK)
+def tensor_core_form(dtype: torch.dtype, kv_rank: int, rot: int) -> bool:
+    """Whether the launcher takes the tensor-core form of the kernel (csrc/latent_attention.cu: bfloat16, kv_rank a
+    multiple of 32 up to 512, kv_rank + rot a multiple of 16; TQ_LATENT_NO_MMA=1 switches it off)."""
+    import os
+    return (dtype == torch.bfloat16 and kv_rank % 32 == 0 and kv_rank <= 512 and (kv_rank + rot) % 16 == 0
+            and os.environ.get("TQ_LATENT_NO_MMA", "") in ("", "0"))
+
+
+def splits_for(n_tokens: int, heads: int, longest: int, device, tensor_cores: bool = False) -> int:
+    """Key ranges per token.  A block walks its range sixteen keys at a time, so a step of few tokens over long
+    ranges is cut until a block has about 64 keys (128 in the tensor-core form, which serves sixteen heads per
+    block instead of four) or the launch has three waves of blocks; prompts (many tokens) are not cut.  The ranges
+    are joined in range order, so a launch shape gives the same bits every time; logits agree across shapes to
+    rounding."""
+    blocks = n_tokens * -(-heads // (16 if tensor_cores else HEADS_PER_BLOCK))
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return int(max(1, min(64, longest // 32, (8 * sms) // blocks)))
+    return int(max(1, min(64, longest // (128 if tensor_cores else 64), (3 * sms) // blocks)))
 
 
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: torch.Tensor, sink: Optional[torch.Tensor],

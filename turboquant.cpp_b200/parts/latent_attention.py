@@ -123,7 +123,7 @@ class LatentAttentionMixer(Mixer):
         the step only, so it runs inside the decode graphs."""
         T, H, R = q_lat.shape
         longest = min(self.window, ctx.max_kv_len) if self.window else ctx.max_kv_len
-        n_splits = KL.splits_for(T, H, longest, q.device)
+        n_splits = KL.splits_for(T, H, longest, q.device, KL.tensor_core_form(q.dtype, R, self.rot_dim))
         partial = torch.empty(T * H * n_splits * (R + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
         KL.latent_attention(q_lat, q, self.dim, cache.kv, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                             cache.page_size, self.window, self.scale, sums, H, R, self.rot_dim, n_splits, partial)
