@@ -54,10 +54,10 @@ CONFIGS = {
                 vocab=61, width=40, eps=1e-6, scale=1.0, bigram=None),
     # wide rows (more than 256 elements), one head, windows wider than a page, four taps
     "c": config([layer("latent_attention", latent(heads=1, dim=32, rot_dim=32, vdim=32, kv_rank=288, window=130, scale=0.2,
-                                                  base=250000.0, scaling={"factor": 2.0, "original": 32, "fast": 32.0, "slow": 1.0}), ff=96),
+                                                  base=500000.0, scaling={"factor": 8.0, "original": 32, "fast": 16.0, "slow": 2.0}), ff=96),
                  layer("mamba2", mamba(heads=2, vdim=40, state=64, groups=1, conv=4, norm_groups=2)),
                  layer("latent_attention", latent(heads=1, dim=32, rot_dim=32, vdim=32, kv_rank=288, window=65, scale=0.2,
-                                                  base=250000.0, kv_from=0))],
+                                                  base=500000.0, scaling={"factor": 8.0, "original": 32, "fast": 16.0, "slow": 2.0}, kv_from=0))],
                 vocab=128, width=64, bigram=(31, 1, 1)),
 }
 

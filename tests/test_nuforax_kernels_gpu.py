@@ -34,12 +34,15 @@ def plain_rows_attention(q_lat, q_rot, rows, R, sink, window, scale, pos):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,R,rot,window,n_ctx", [(3, 40, 8, 37, 300), (5, 288, 32, 0, 700), (1, 30, 6, 64, 130),
-                                                   (4, 96, 32, 65, 200), (2, 512, 64, 129, 400)])
-def test_latent_attention_with_one_key_that_stands_out(dtype, H, R, rot, window, n_ctx):
+@pytest.mark.parametrize("H,R,rot,window,n_ctx,lead", [
+    (3, 40, 8, 37, 300, 5), (5, 288, 32, 0, 700, 8), (1, 30, 6, 64, 130, 5), (6, 160, 32, 65, 200, 8), (6, 160, 32, 65, 200, 5),
+    (2, 512, 64, 129, 400, 8), (20, 64, 16, 50, 300, 6), (17, 32, 0, 33, 100, 8)])
+def test_latent_attention_with_one_key_that_stands_out(dtype, H, R, rot, window, n_ctx, lead):
     """Queries at several positions; for each, one key is given a score far above the rest: the key just inside
     the window, the key just outside it, a key at a page's first or last place, the first key of the sequence.
-    Outside the window (or with a sink above it) the result must not move; inside it must follow the key."""
+    Outside the window (or with a sink above it) the result must not move; inside it must follow the key.
+    `lead` plain dimensions stand in front of a head's rotated ones (8: rows the kernels can copy 16 bytes at a
+    time; 5: an odd head size, which keeps bfloat16 off the tensor-core form; 6: that form with single copies)."""
     from turboquant_cpp_b200.kernels import latent_attention as KL
     rng = np.random.default_rng(R + window)
     page_size, n_pages = 64, 16
@@ -71,15 +74,15 @@ def test_latent_attention_with_one_key_that_stands_out(dtype, H, R, rot, window,
         hh = min(1, H - 1)
         q_lat[hh] = rows[j, :R] * (12.0 / scale / max(1e-9, (rows[j, :R] ** 2).sum()))
         ql = dev(q_lat[None], dtype)
-        qfull = torch.zeros((1, H * (5 + rot)), dtype=dtype, device=DEV)          # 5 plain dimensions in front
-        qfull.view(1, H, 5 + rot)[:, :, 5:] = dev(q_rot[None], dtype)
+        qfull = torch.zeros((1, H * (lead + rot)), dtype=dtype, device=DEV)          # plain dimensions in front
+        qfull.view(1, H, lead + rot)[:, :, lead:] = dev(q_rot[None], dtype)
         ref = plain_rows_attention(ql[0].float().cpu().numpy().astype(np.float64),
-                                   qfull.view(H, 5 + rot)[:, 5:].float().cpu().numpy().astype(np.float64), rows, R, sink,
+                                   qfull.view(H, lead + rot)[:, lead:].float().cpu().numpy().astype(np.float64), rows, R, sink,
                                    window, scale, p)
         for n_splits in (1, 3, 7):
             out = torch.empty((1, H, R), dtype=dtype, device=DEV)
             partial = torch.empty(H * n_splits * (R + 2), dtype=torch.float32, device=DEV)
-            KL.latent_attention(ql, qfull, 5, cache, dev(sink), i32([p]), i32([0]), table, page_size, window, scale, out, H,
+            KL.latent_attention(ql, qfull, lead, cache, dev(sink), i32([p]), i32([0]), table, page_size, window, scale, out, H,
                                 R, rot, n_splits, partial)
             err = np.abs(out[0].float().cpu().numpy() - ref).max() / np.abs(ref).max()
             assert err < tol, f"position {p}, key {j} ({tag}), {n_splits} ranges: {err:.2e}"
@@ -169,7 +172,7 @@ def test_convolution_and_recurrence_carry_their_state_over_steps(heads, vdim, N,
     rng = np.random.default_rng(N + taps)
     inner, gn = heads * vdim, groups * N
     C, Pr = inner + 2 * gn, 2 * inner + 2 * gn + heads
-    lens = {0: 41, 1: 23}
+    lens = {0: 341, 1: 28}
     proj = {s: dev(rng.standard_normal((n, Pr))).cpu().numpy().astype(np.float64) for s, n in lens.items()}
     w_conv, b_conv = rng.standard_normal((C, taps)) * 0.5, rng.standard_normal(C) * 0.3
     dt_bias, a_log, d_skip = rng.standard_normal(heads), rng.standard_normal(heads) * 0.5, rng.standard_normal(heads)
@@ -184,9 +187,9 @@ def test_convolution_and_recurrence_carry_their_state_over_steps(heads, vdim, N,
     n_slots, kept_size = 4, (taps - 1) * C
     st = torch.zeros((n_slots, kept_size + heads * N * vdim), dtype=torch.float32, device=DEV)
     kept = st[:, :kept_size].unflatten(1, (taps - 1, C))
-    S = st[:, kept_size:].unflatten(1, (heads, N, vdim))
+    S = st[:, kept_size:].unflatten(1, (heads, vdim, N))
     slots = {0: 3, 1: 1}
-    cuts = [(1, 2), (2, 1), (17, 1), (1, 17), (20, 2)]
+    cuts = [(1, 2), (2, 1), (17, 1), (300, 5), (1, 17), (20, 2)]     # the long step takes the form with several tokens a thread
     at = {0: 0, 1: 0}
     for n0, n1 in cuts:
         pr = dev(np.concatenate([proj[0][at[0]:at[0] + n0], proj[1][at[1]:at[1] + n1]]))

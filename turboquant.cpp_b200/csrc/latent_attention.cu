@@ -295,15 +295,18 @@ latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, 
 // ---------------------------------------------------------------------------------------
 // The same on tensor cores (bfloat16, R a multiple of 32 up to 512, R + rot a multiple of 16): the block's sixteen
 // heads are the sixteen rows of mma.sync m16n8k16, so one cached row serves sixteen dot products per
-// instruction.  Keys come in tiles of sixteen through shared memory.  Every warp computes the tile's scores
-// (16 heads x 16 keys, fp32 accumulators; scale, mask and the online softmax on the accumulator fragments) and
-// owns a quarter of the R output columns, for which it multiplies the weights (rounded to bfloat16, as the
-// second operand's type demands) with the tile's rows; computing the scores four times over costs less than
-// passing them between warps, and leaves no barrier inside a tile.
+// instruction.  Keys come in tiles of 32 through a two-stage ring in shared memory, filled by 16-byte cp.async
+// copies a tile ahead.  Of a tile's scores (16 heads x 32 keys) every warp computes the eight keys that are its
+// own (fp32 accumulators; scale and mask on the fragments) and leaves them in shared memory; after a barrier
+// every warp reads all of them, keeps the online softmax of its two rows (all warps the same numbers) and
+// multiplies the weights, rounded to bfloat16 as the second operand's type demands, with the tile's rows for the
+// quarter of the R output columns that it owns.  Fragments come from shared memory by ldmatrix (transposed for
+// the rows as values).
 // ---------------------------------------------------------------------------------------
 #define LATM_HEADS 16
-#define LATM_KEYS 16
-#define LATM_PAD 8            // bfloat16 elements between rows in shared memory: fragment reads hit 32 different banks
+#define LATM_KEYS 32
+#define LATM_PAD 8            // bfloat16 elements between rows in shared memory: eight rows' 16-byte pieces hit all banks
+#define LATM_PS 40            // floats per row of the scores' exchange area
 
 __device__ __forceinline__ void lat_mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -313,6 +316,23 @@ __device__ __forceinline__ void lat_mma16816(float* c, const uint32_t* a, uint32
 __device__ __forceinline__ uint32_t lat_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void lat_ldsm4(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+}
+__device__ __forceinline__ void lat_ldsm2(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+}
+__device__ __forceinline__ void lat_ldsm4_t(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+}
+// 16 bytes global -> shared, or 16 zero bytes when `bytes` is 0 (the source is not read then)
+__device__ __forceinline__ void lat_cp16(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                 ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
 template <int OT>      // output n-tiles (of 8 columns) per warp: R = 32 * OT
@@ -328,100 +348,149 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     extern __shared__ uint4 latm_smem[];
     const int Dk = R + rot, ld = Dk + LATM_PAD;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(latm_smem);       // [16 heads][ld]
-    __nv_bfloat16* Ks = Qs + LATM_HEADS * ld;                               // [16 keys][ld]
+    __nv_bfloat16* Ks = Qs + LATM_HEADS * ld;                               // [2][32 keys][ld]
+    float* Ps = reinterpret_cast<float*>(Ks + 2 * LATM_KEYS * ld);          // [16 heads][LATM_PS]
     const int t = blockIdx.x, h0 = blockIdx.y * LATM_HEADS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tq = lane & 3;
-    for (int k = threadIdx.x; k < LATM_HEADS * Dk; k += blockDim.x) {
-        const int r = k / Dk, e = k - r * Dk, h = h0 + r;
-        __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-        if (h < H) v = e < R ? q_lat[((size_t)t * H + h) * R + e] : q[((size_t)t * H + h) * q_dim + q_off + (e - R)];
-        Qs[r * ld + e] = v;
-    }
+    const int chunks = Dk / 8;                                              // 16-byte pieces of a row
     const int pos = positions[t];
     const int first = window > 0 ? max(0, pos + 1 - window) : 0;
     const int n_keys = pos + 1 - first;
     const int per = (n_keys + (int)gridDim.z - 1) / (int)gridDim.z;
     const int lo = first + (int)blockIdx.z * per, hi = min(pos + 1, lo + per);
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
-    const int chunks = Dk / 8;                                              // 16-byte pieces of a row
+
+    // a tile's rows go round the warps; a lane copies every 32nd piece of a row (rows beyond the range as zeros)
+    auto fetch = [&](int p0, __nv_bfloat16* dst) {
+        for (int r = warp; r < LATM_KEYS; r += LAT_WARPS) {
+            const int p = p0 + r;
+            const __nv_bfloat16* src = cache;
+            int bytes = 0;
+            if (p < hi) {
+                const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+                src = cache + ((size_t)page * page_size + p % page_size) * Dk;
+                bytes = 16;
+            }
+            for (int c = lane; c < chunks; c += 32) lat_cp16(dst + r * ld + 8 * c, bytes ? src + 8 * c : src, bytes);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (lo < hi) fetch(lo, Ks);
+    {   // the heads' queries, 16 bytes at a time (heads beyond H as zeros)
+        const int rc = rot / 8, lc = R / 8;
+        const bool rot_vec = (q_dim % 8 == 0) && (q_off % 8 == 0);
+        for (int k = threadIdx.x; k < LATM_HEADS * lc; k += blockDim.x) {
+            const int r = k / lc, c = k - r * lc, h = h0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (h < H) v = reinterpret_cast<const uint4*>(q_lat + ((size_t)t * H + h) * R)[c];
+            *reinterpret_cast<uint4*>(Qs + r * ld + 8 * c) = v;
+        }
+        if (rot_vec) {
+            for (int k = threadIdx.x; k < LATM_HEADS * rc; k += blockDim.x) {
+                const int r = k / rc, c = k - r * rc, h = h0 + r;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (h < H) v = reinterpret_cast<const uint4*>(q + ((size_t)t * H + h) * q_dim + q_off)[c];
+                *reinterpret_cast<uint4*>(Qs + r * ld + R + 8 * c) = v;
+            }
+        } else {
+            for (int k = threadIdx.x; k < LATM_HEADS * rot; k += blockDim.x) {
+                const int r = k / rot, e = k - r * rot, h = h0 + r;
+                Qs[r * ld + R + e] = h < H ? q[((size_t)t * H + h) * q_dim + q_off + e] : __float2bfloat16_rn(0.f);
+            }
+        }
+    }
 
     float o[OT][4];
 #pragma unroll
     for (int j = 0; j < OT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};                 // rows g and g + 8
     const int col_base = warp * OT * 8;
+    // ldmatrix addresses: the queries' 16 x 16 piece (lane i: row i % 16, second eight columns for i >= 16), this
+    // warp's eight keys (lane i: key i % 8, columns 8 * (i / 8) on), a tile's 32 rows as values (lane i: row i)
+    const __nv_bfloat16* qa = Qs + (lane & 15) * ld + 8 * (lane >> 4);
+    const int kb_off = (8 * warp + (lane & 7)) * ld + 8 * (lane >> 3);
+    const int ksteps = Dk / 16;
 
-    for (int p0 = lo; p0 < hi; p0 += LATM_KEYS) {
-        __syncthreads();                                                    // the tile before has been used (and Qs is written)
-        for (int k = threadIdx.x; k < LATM_KEYS * chunks; k += blockDim.x) {
-            const int r = k / chunks, c = k - r * chunks, p = p0 + r;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (p < hi) {
-                const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
-                v = reinterpret_cast<const uint4*>(cache + ((size_t)page * page_size + p % page_size) * Dk)[c];
-            }
-            *reinterpret_cast<uint4*>(Ks + r * ld + 8 * c) = v;
+    int stage = 0;
+    for (int p0 = lo; p0 < hi; p0 += LATM_KEYS, stage ^= 1) {
+        const __nv_bfloat16* Kt = Ks + stage * LATM_KEYS * ld;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                          // the tile has landed for all; the other stage and Ps are free
+        if (p0 + LATM_KEYS < hi) fetch(p0 + LATM_KEYS, Ks + (stage ^ 1) * LATM_KEYS * ld);
+        // scores of this warp's eight keys: two chains of accumulators, joined at the end
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        int ks = 0;
+        for (; ks + 2 <= ksteps; ks += 2) {
+            uint32_t a0[4], a1[4], b[4];
+            lat_ldsm4(a0, qa + 16 * ks);
+            lat_ldsm4(a1, qa + 16 * ks + 16);
+            lat_ldsm4(b, Kt + kb_off + 16 * ks);
+            lat_mma16816(sa, a0, b[0], b[1]);
+            lat_mma16816(sb, a1, b[2], b[3]);
+        }
+        if (ks < ksteps) {
+            uint32_t a0[4], b[2];
+            lat_ldsm4(a0, qa + 16 * ks);
+            lat_ldsm2(b, Kt + kb_off + 16 * ks);      // lanes 0..15 give the addresses: columns 16 ks and 16 ks + 8
+            lat_mma16816(sa, a0, b[0], b[1]);
+        }
+        {   // this lane holds keys 8 warp + 2 tq + {0, 1} of rows g (values 0, 1) and g + 8 (values 2, 3)
+            const int kc = 8 * warp + 2 * tq;
+            const bool s0 = p0 + kc < hi, s1 = p0 + kc + 1 < hi;
+            float2 top, bot;
+            top.x = s0 ? (sa[0] + sb[0]) * scale : -INFINITY;
+            top.y = s1 ? (sa[1] + sb[1]) * scale : -INFINITY;
+            bot.x = s0 ? (sa[2] + sb[2]) * scale : -INFINITY;
+            bot.y = s1 ? (sa[3] + sb[3]) * scale : -INFINITY;
+            *reinterpret_cast<float2*>(Ps + g * LATM_PS + kc) = top;
+            *reinterpret_cast<float2*>(Ps + (g + 8) * LATM_PS + kc) = bot;
         }
         __syncthreads();
-        // scores: 16 heads x 16 keys
-        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        for (int k0 = 0; k0 < Dk; k0 += 16) {
-            uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * ld + k0 + 2 * tq);
-            a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * ld + k0 + 2 * tq);
-            a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * ld + k0 + 2 * tq + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * ld + k0 + 2 * tq + 8);
+        // all 32 scores of rows g and g + 8, in the first operand's layout: sc[r][2 i + {0, 1}] = keys 8 i + 2 tq + {0, 1}
+        float sc[2][8];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const __nv_bfloat16* kp = Ks + (nt * 8 + g) * ld + k0 + 2 * tq;
-                lat_mma16816(sc[nt], a, *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
-            }
-        }
-        // scale, mask, online softmax: this lane holds keys nt*8 + 2*tq + {0,1} of rows g (values 0,1) and g+8 (values 2,3)
-        float tmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int r = 0; r < 2; ++r) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const bool seen = p0 + nt * 8 + 2 * tq + (i & 1) < hi;
-                sc[nt][i] = seen ? sc[nt][i] * scale : -INFINITY;
-                tmax[i >> 1] = fmaxf(tmax[i >> 1], sc[nt][i]);
+                const float2 v = *reinterpret_cast<const float2*>(Ps + (g + 8 * r) * LATM_PS + 8 * i + 2 * tq);
+                sc[r][2 * i] = v.x;
+                sc[r][2 * i + 1] = v.y;
             }
         }
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-            const float m_new = fmaxf(m[r], tmax[r]);          // finite: a tile has at least one key
+            float tmax = sc[r][0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) tmax = fmaxf(tmax, sc[r][i]);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_new = fmaxf(m[r], tmax);             // finite: a tile has at least one key
             corr[r] = expf(m[r] - m_new);                       // exp(-inf) = 0 on the first tile
             m[r] = m_new;
             l[r] *= corr[r];
-        }
-        uint32_t pa[4];
-        {
-            float pe[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    pe[nt][i] = expf(sc[nt][i] - m[i >> 1]);
-                    l[i >> 1] += pe[nt][i];                     // this lane's share; the quad's shares are added at the end
-                }
+            for (int i = 0; i < 8; ++i) {
+                sc[r][i] = expf(sc[r][i] - m_new);
+                l[r] += sc[r][i];                               // this lane's share; the quad's shares are added at the end
             }
-            pa[0] = lat_pack(pe[0][0], pe[0][1]);
-            pa[1] = lat_pack(pe[0][2], pe[0][3]);
-            pa[2] = lat_pack(pe[1][0], pe[1][1]);
-            pa[3] = lat_pack(pe[1][2], pe[1][3]);
         }
-        const unsigned short* Ku = reinterpret_cast<const unsigned short*>(Ks);
+        uint32_t pa[2][4];                                      // keys 0..15 and 16..31
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) {
+            pa[k2][0] = lat_pack(sc[0][4 * k2], sc[0][4 * k2 + 1]);
+            pa[k2][1] = lat_pack(sc[1][4 * k2], sc[1][4 * k2 + 1]);
+            pa[k2][2] = lat_pack(sc[0][4 * k2 + 2], sc[0][4 * k2 + 3]);
+            pa[k2][3] = lat_pack(sc[1][4 * k2 + 2], sc[1][4 * k2 + 3]);
+        }
+        const __nv_bfloat16* va = Kt + lane * ld + col_base;
 #pragma unroll
         for (int j = 0; j < OT; ++j) {
             o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
-            const int col = col_base + j * 8 + g;
-            const uint32_t b0 = (uint32_t)Ku[(2 * tq) * ld + col] | ((uint32_t)Ku[(2 * tq + 1) * ld + col] << 16);
-            const uint32_t b1 = (uint32_t)Ku[(2 * tq + 8) * ld + col] | ((uint32_t)Ku[(2 * tq + 9) * ld + col] << 16);
-            lat_mma16816(o[j], pa, b0, b1);
+            uint32_t b[4];
+            lat_ldsm4_t(b, va + 8 * j);
+            lat_mma16816(o[j], pa[0], b[0], b[1]);
+            lat_mma16816(o[j], pa[1], b[2], b[3]);
         }
     }
 #pragma unroll
@@ -447,37 +516,52 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
             float* pp = partial + (((size_t)t * H + h) * gridDim.z + blockIdx.z) * (R + 2);
             if (warp == 0 && tq == 0) { pp[0] = m[r]; pp[1] = l[r]; }       // an empty range leaves -inf and 0
 #pragma unroll
-            for (int j = 0; j < OT; ++j) {
-                pp[2 + col_base + j * 8 + 2 * tq] = o[j][2 * r];
-                pp[2 + col_base + j * 8 + 2 * tq + 1] = o[j][2 * r + 1];
-            }
+            for (int j = 0; j < OT; ++j)
+                *reinterpret_cast<float2*>(pp + 2 + col_base + j * 8 + 2 * tq) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
         }
     }
 }
 
-// joins the ranges of one (token, head) in range order and lets the sink take part
+// joins the ranges of one (token, head) in range order and lets the sink take part: the first warp turns the
+// ranges' maxima and sums into one weight per range (the sink only adds to the denominator), then every thread
+// adds up its elements over the ranges
+#define LAT_MAX_SPLITS 64
 template <typename TA>
 __global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, int n_splits,
                                     int H, int R, TA* __restrict__ out) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float wgt[LAT_MAX_SPLITS];
     const int t = blockIdx.x, h = blockIdx.y;
     const float* pp = partial + ((size_t)t * H + h) * n_splits * (R + 2);
-    const float sk = sink ? sink[h] : -INFINITY;
-    float M = sk;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, pp[(size_t)s * (R + 2)]);
-    float L = sink ? expf(sk - M) : 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = pp[(size_t)s * (R + 2)];
-        if (ms != -INFINITY) L += pp[(size_t)s * (R + 2) + 1] * expf(ms - M);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float sk = sink ? sink[h] : -INFINITY;
+        float ms[LAT_MAX_SPLITS / 32], ls[LAT_MAX_SPLITS / 32], M = sk;
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_SPLITS / 32; ++i) {
+            const int s = lane + 32 * i;
+            ms[i] = s < n_splits ? pp[(size_t)s * (R + 2)] : -INFINITY;
+            ls[i] = s < n_splits ? pp[(size_t)s * (R + 2) + 1] : 0.f;
+            M = fmaxf(M, ms[i]);
+        }
+        M = tq_warp_max(M);                              // finite: some range holds a key
+        float L = 0.f;
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_SPLITS / 32; ++i) {
+            ms[i] = ms[i] == -INFINITY ? 0.f : expf(ms[i] - M);
+            L += ls[i] * ms[i];
+        }
+        L = tq_warp_sum(L) + (sink ? expf(sk - M) : 0.f);
+#pragma unroll
+        for (int i = 0; i < LAT_MAX_SPLITS / 32; ++i) wgt[lane + 32 * i] = ms[i] / L;
     }
+    __syncthreads();
     for (int e = threadIdx.x; e < R; e += blockDim.x) {
         float v = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = pp[(size_t)s * (R + 2)];
-            if (ms != -INFINITY) v += pp[(size_t)s * (R + 2) + 2 + e] * expf(ms - M);
-        }
-        out[((size_t)t * H + h) * R + e] = tq_from_float<TA>(v / L);
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) v += pp[(size_t)s * (R + 2) + 2 + e] * wgt[s];
+        out[((size_t)t * H + h) * R + e] = tq_from_float<TA>(v);
     }
 }
 
@@ -502,20 +586,31 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
     TQ_REQUIRE(H >= 1 && R >= 1 && rot >= 0 && Dk <= LAT_MAX_ROW, "latent_attention: a row of %d + %d elements exceeds %d",
                R, rot, LAT_MAX_ROW);
     TQ_REQUIRE(window >= 0, "latent_attention: negative window %d", window);
-    TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || partial), "latent_attention: %d key ranges need a "
-               "scratch buffer", n_splits);
+    TQ_REQUIRE(n_splits >= 1 && n_splits <= LAT_MAX_SPLITS && (n_splits == 1 || partial), "latent_attention: %d key ranges "
+               "(at most %d, and more than one need a scratch buffer)", n_splits, LAT_MAX_SPLITS);
     TQ_REQUIRE((H + LAT_HG - 1) / LAT_HG <= 65535, "latent_attention: %d heads exceed the grid limit", H);
     TQ_REQUIRE(rot == 0 || (q && q_off >= 0 && q_off + rot <= q_dim), "latent_attention: the queries' rotated part does not fit");
     const bool mma = act_dtype == TQ_BF16 && Dk % 16 == 0 && R % 32 == 0 && R <= 512 && (q_dim % 2 == 0) &&
-                     ((uintptr_t)cache % 16) == 0 && ((uintptr_t)out % 4) == 0 && lat_use_mma();
+                     ((uintptr_t)cache % 16) == 0 && ((uintptr_t)out % 4) == 0 && ((uintptr_t)q_lat % 16) == 0 &&
+                     ((uintptr_t)q % 16) == 0 && (!partial || ((uintptr_t)partial % 8) == 0) && lat_use_mma();
     if (mma) {
         dim3 grid(T_, (H + LATM_HEADS - 1) / LATM_HEADS, n_splits);
         TQ_REQUIRE(grid.y <= 65535, "latent_attention: %d heads exceed the grid limit", H);
-        const size_t smem = (size_t)(LATM_HEADS + LATM_KEYS) * (Dk + LATM_PAD) * sizeof(__nv_bfloat16);
+        const size_t smem = (size_t)(LATM_HEADS + 2 * LATM_KEYS) * (Dk + LATM_PAD) * sizeof(__nv_bfloat16) +
+                            (size_t)LATM_HEADS * LATM_PS * sizeof(float);
 #define LATM_LAUNCH(OT_)                                                                                           \
-        tq_launch(grid, LAT_WARPS * 32, smem, stream)(latent_attention_mma_kernel<OT_>, (const __nv_bfloat16*)q_lat,   \
-            (const __nv_bfloat16*)q, q_dim, q_off, (const __nv_bfloat16*)cache, sink, positions, seq_of_token, page_table, \
-            table_stride, page_size, window, scale, (__nv_bfloat16*)out, partial, H, R, rot, n_seqs, n_pages)
+        do {                                                                                                       \
+            auto kern = latent_attention_mma_kernel<OT_>;                                                          \
+            static size_t allowed = 48 * 1024;                                                                     \
+            if (smem > allowed) {                                                                                  \
+                cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+                if (e != cudaSuccess) TQ_FAIL(-1, "latent_attention: %d bytes of shared memory refused: %s", (int)smem, cudaGetErrorString(e)); \
+                allowed = smem;                                                                                    \
+            }                                                                                                      \
+            tq_launch(grid, LAT_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q_lat,                       \
+                (const __nv_bfloat16*)q, q_dim, q_off, (const __nv_bfloat16*)cache, sink, positions, seq_of_token, page_table, \
+                table_stride, page_size, window, scale, (__nv_bfloat16*)out, partial, H, R, rot, n_seqs, n_pages); \
+        } while (0)
         const int OT = R / 32;
         if (OT <= 2) { if (OT == 1) LATM_LAUNCH(1); else LATM_LAUNCH(2); }
         else if (OT <= 4) { if (OT == 3) LATM_LAUNCH(3); else LATM_LAUNCH(4); }

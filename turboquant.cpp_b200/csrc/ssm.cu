@@ -11,6 +11,8 @@
 //   conv_state_update  the kept inputs after the step (a launch of its own: conv_silu reads the old ones)
 //   ssm_scan           the recurrence over each sequence's run of new tokens, a warp per four columns of the state
 //   gated_group_norm   y * silu(z), RMS norm in equal groups, weight
+#include <type_traits>
+
 #include "common.cuh"
 
 TQ_DEFINE_LAST_ERROR
@@ -18,25 +20,48 @@ TQ_DEFINE_LAST_ERROR
 #define SSM_MAX_TAPS 8
 #define SSM_MAX_STATE 256
 
+#define CONV_TOKENS 8          // consecutive tokens of a long step per thread: an input is read once, not once per tap
+
 template <typename TW>
 __global__ void conv_silu_kernel(const float* __restrict__ proj, int P, int off, const TW* __restrict__ w,
                                  const TW* __restrict__ b, const float* __restrict__ kept, long long slot_stride,
-                                 float* __restrict__ out, int C, int taps, const int* __restrict__ seq_of_token,
+                                 float* __restrict__ out, int T_, int C, int taps, int per_thread, const int* __restrict__ seq_of_token,
                                  const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int n_seqs) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int tb = blockIdx.x * per_thread, c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    const int s = TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE);
-    const int i = t - cu_seqlens[s];                 // place in the sequence's run of new tokens
-    const float* old = kept + (size_t)slots[s] * slot_stride;      // [taps-1][C]: inputs of the positions just before the run
-    float acc = b ? tq_to_float(b[c]) : 0.f;
-    for (int k = 0; k < taps; ++k) {
-        const int back = taps - 1 - k, src = i - back;
-        const float v = src >= 0 ? proj[(size_t)(t - back) * P + off + c] : old[(size_t)(taps - 1 + src) * C + c];
-        acc += tq_to_float(w[(size_t)c * taps + k]) * v;
+    // win[SSM_MAX_TAPS - 1 - k] is the input k positions back; wr the tap that meets it (0 beyond the taps)
+    float win[SSM_MAX_TAPS], wr[SSM_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < SSM_MAX_TAPS; ++k) {
+        win[SSM_MAX_TAPS - 1 - k] = 0.f;
+        wr[SSM_MAX_TAPS - 1 - k] = k < taps ? tq_to_float(w[(size_t)c * taps + taps - 1 - k]) : 0.f;
     }
-    out[(size_t)t * C + c] = acc / (1.0f + expf(-acc));
+    const float bias = b ? tq_to_float(b[c]) : 0.f;
+    const int t_end = min(T_, tb + per_thread);
+    for (int t = tb; t < t_end; ++t) {
+        const int s = TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE);
+        const int i = t - cu_seqlens[s];             // place in the sequence's run of new tokens
+        if (t == tb || i == 0) {                     // the thread's first token, or a new sequence: the inputs before it
+            const float* old = kept + (size_t)slots[s] * slot_stride;      // [taps-1][C]: inputs of the positions just before the run
+#pragma unroll
+            for (int k = 1; k < SSM_MAX_TAPS; ++k) {
+                if (k < taps) {
+                    const int src = i - k;
+                    win[SSM_MAX_TAPS - 1 - k] = src >= 0 ? proj[(size_t)(t - k) * P + off + c]
+                                                         : old[(size_t)(taps - 1 + src) * C + c];
+                }
+            }
+        }
+        win[SSM_MAX_TAPS - 1] = proj[(size_t)t * P + off + c];
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < SSM_MAX_TAPS; ++k) acc += wr[k] * win[k];
+        out[(size_t)t * C + c] = acc / (1.0f + expf(-acc));
+#pragma unroll
+        for (int k = 0; k < SSM_MAX_TAPS - 1; ++k) win[k] = win[k + 1];
+    }
 }
 
 __global__ void conv_state_update_kernel(const float* __restrict__ proj, int P, int off, float* __restrict__ kept,
@@ -68,11 +93,12 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
     TQ_REQUIRE(C >= 1 && taps >= 1 && taps <= SSM_MAX_TAPS, "conv_silu: %d taps (1..%d)", taps, SSM_MAX_TAPS);
     TQ_REQUIRE(off >= 0 && off + C <= P, "conv_silu: channels %d..%d outside the projection's %d", off, off + C, P);
     const int threads = 128;
-    dim3 grid(T_, (C + threads - 1) / threads);
+    const int per_thread = T_ >= 256 ? CONV_TOKENS : 1;        // short steps keep a thread per token and channel
+    dim3 grid((T_ + per_thread - 1) / per_thread, (C + threads - 1) / threads);
     TQ_REQUIRE(grid.y <= 65535, "conv_silu: %d channels exceed the grid limit", C);
     TQ_DISPATCH(w_dtype, TW,
         (tq_launch(grid, threads, 0, stream)(conv_silu_kernel<TW>, proj, P, off, (const TW*)w, (const TW*)b,
-                                             (const float*)kept, slot_stride, out, C, taps, seq_of_token, cu_seqlens, slots, n_seqs)));
+                                             (const float*)kept, slot_stride, out, T_, C, taps, per_thread, seq_of_token, cu_seqlens, slots, n_seqs)));
     TQ_CHECK_LAUNCH("conv_silu");
     if (taps > 1) {
         dim3 ugrid(n_seqs, (C + threads - 1) / threads);
@@ -84,17 +110,19 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
 
 // ---------------------------------------------------------------------------------------
 // ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_WARPS warps per block.  A warp owns SSM_CPW
-// neighbouring columns of the head's state: lane l keeps rows l, l+32, ... (RPL of them) of each column in
-// registers for the whole run, so a step reads its B and C values once for the four columns, does RPL x 4
-// multiply-adds for the state and as many for y, and sums the four y over the warp's lanes with six shuffles
-// (the lanes halve the set of columns they carry twice, then add up within groups of eight).  No barrier
-// between steps.  The run is walked in chunks of TC steps whose B, C, x, step sizes and decays lie in shared
-// memory (rows beyond N as zeros, so the state's padding rows stay zero and need no test); a chunk's inputs are
-// fetched into registers, all loads in flight together, while the chunk before is being computed.
+// neighbouring columns of the head's state (kept column by column, [vdim][N], so the lanes' loads and stores are
+// neighbours in memory): lane l keeps rows l, l+32, ... (RPL of them) of each column in registers for the whole run, so a step reads its B and C values once for the four columns and does RPL x 4
+// multiply-adds for the state and as many for y.  The sums of y over the lanes are not taken step by step: eight
+// steps leave 32 partial sums per lane, which five rounds of exchanges (31 shuffles) turn into one whole sum per
+// lane, so the chain of dependent shuffles is paid once per eight steps and the state's updates run on
+// meanwhile.  No barrier between steps.  The run is walked in chunks of TC steps whose B, C, x, step sizes and
+// decays lie in shared memory (rows beyond N as zeros, so the state's padding rows stay zero and need no test); a
+// chunk's inputs are fetched into registers, all loads in flight together, while the chunk before is computed.
 // ---------------------------------------------------------------------------------------
 #define SSM_WARPS 8
 #define SSM_CPW 4
 #define SSM_COLS (SSM_WARPS * SSM_CPW)
+#define SSM_GROUP 8           // steps whose sums over the lanes are taken together; SSM_GROUP * SSM_CPW is a warp's 32 lanes
 
 template <typename TW, int RPL, int TC>
 __global__ void __launch_bounds__(32 * SSM_WARPS)
@@ -127,7 +155,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
 #pragma unroll
         for (int c = 0; c < SSM_CPW; ++c) {
             const int row = lane + 32 * r;
-            S[r][c] = (row < N && vw + c < vdim) ? Sg[(size_t)row * vdim + vw + c] : 0.f;
+            S[r][c] = (row < N && vw + c < vdim) ? Sg[(size_t)(vw + c) * N + row] : 0.f;
         }
     }
     constexpr int LPT = TC * NP / NT;                    // B and C values per thread and chunk
@@ -153,8 +181,6 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
         if (tid < tc) praw = proj[(size_t)(first + t0 + tid) * P + dt_off + h];
     };
     if (n > 0) fetch(0);
-    const bool hi16 = lane & 16, hi8 = lane & 8;
-    const int my_col = (hi16 ? 2 : 0) + (hi8 ? 1 : 0);   // the column whose sum this lane ends up with
     for (int t0 = 0; t0 < n; t0 += TC) {
         const int tc = min(TC, n - t0);
 #pragma unroll
@@ -172,33 +198,48 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
         }
         __syncthreads();
         if (t0 + TC < n) fetch(t0 + TC);
-#pragma unroll 2
-        for (int tt = 0; tt < tc; ++tt) {
-            const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * SSM_COLS + warp * SSM_CPW);
-            const float xv[SSM_CPW] = {x4.x, x4.y, x4.z, x4.w};
-            const float a = dec[tt], dt = dts[tt];
-            float acc[SSM_CPW] = {0.f, 0.f, 0.f, 0.f};
+        for (int t8 = 0; t8 < tc; t8 += SSM_GROUP) {
+            // SSM_GROUP steps' partial sums of y (this lane's rows) are kept and added up over the lanes together
+            float v[SSM_GROUP * SSM_CPW];
+            auto steps = [&](auto full) {        // a whole group runs as straight-line code: its loads can go ahead
 #pragma unroll
-            for (int r = 0; r < RPL; ++r) {
-                const float bv = Bs[tt * NP + lane + 32 * r] * dt, cv = Cs[tt * NP + lane + 32 * r];
+                for (int j = 0; j < SSM_GROUP; ++j) {
+                    const int tt = t8 + j;
 #pragma unroll
-                for (int c = 0; c < SSM_CPW; ++c) {
-                    S[r][c] = a * S[r][c] + bv * xv[c];
-                    acc[c] += S[r][c] * cv;
+                    for (int c = 0; c < SSM_CPW; ++c) v[j * SSM_CPW + c] = 0.f;
+                    if (decltype(full)::value || tt < tc) {          // the same for the whole block
+                        const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * SSM_COLS + warp * SSM_CPW);
+                        const float xv[SSM_CPW] = {x4.x, x4.y, x4.z, x4.w};
+                        const float a = dec[tt], dt = dts[tt];
+#pragma unroll
+                        for (int r = 0; r < RPL; ++r) {
+                            const float bv = Bs[tt * NP + lane + 32 * r] * dt, cv = Cs[tt * NP + lane + 32 * r];
+#pragma unroll
+                            for (int c = 0; c < SSM_CPW; ++c) {
+                                S[r][c] = a * S[r][c] + bv * xv[c];
+                                v[j * SSM_CPW + c] += S[r][c] * cv;
+                            }
+                        }
+                    }
+                }
+            };
+            if (t8 + SSM_GROUP <= tc) steps(std::true_type{});
+            else steps(std::false_type{});
+            // 32 sums over 32 lanes: every round a lane keeps the half of its values that its bit names and gets
+            // the other lane's share of that half, so after five rounds lane l holds the whole sum number l
+#pragma unroll
+            for (int half = 16; half >= 1; half >>= 1) {
+                const bool up = lane & half;
+#pragma unroll
+                for (int i = 0; i < half; ++i) {
+                    const float keep = up ? v[i + half] : v[i], send = up ? v[i] : v[i + half];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
                 }
             }
-            // lanes with bit 4 clear go on with columns 0 and 1, the others with 2 and 3; then bit 3 picks one
-            float k0 = hi16 ? acc[2] : acc[0], k1 = hi16 ? acc[3] : acc[1];
-            k0 += __shfl_xor_sync(0xffffffffu, hi16 ? acc[0] : acc[2], 16);
-            k1 += __shfl_xor_sync(0xffffffffu, hi16 ? acc[1] : acc[3], 16);
-            float k = hi8 ? k1 : k0;
-            k += __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
-            k += __shfl_xor_sync(0xffffffffu, k, 4);
-            k += __shfl_xor_sync(0xffffffffu, k, 2);
-            k += __shfl_xor_sync(0xffffffffu, k, 1);
-            const float xm = hi16 ? (hi8 ? xv[3] : xv[2]) : (hi8 ? xv[1] : xv[0]);
-            if ((lane & 7) == 0 && vw + my_col < vdim)
-                y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + vw + my_col] = k + D * xm;
+            const int tt = t8 + (lane >> 2), c = lane & 3;          // SSM_GROUP * SSM_CPW == 32
+            if (tt < tc && vw + c < vdim)
+                y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + vw + c] =
+                    v[0] + D * xs[tt * SSM_COLS + warp * SSM_CPW + c];
         }
         __syncthreads();
     }
@@ -207,7 +248,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
 #pragma unroll
         for (int c = 0; c < SSM_CPW; ++c) {
             const int row = lane + 32 * r;
-            if (row < N && vw + c < vdim) Sg[(size_t)row * vdim + vw + c] = S[r][c];
+            if (row < N && vw + c < vdim) Sg[(size_t)(vw + c) * N + row] = S[r][c];
         }
     }
 }
@@ -229,13 +270,13 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
     TQ_REQUIRE(dt_off >= 0 && dt_off + heads <= P, "ssm_scan: the step sizes lie outside the projection");
     const int RPL = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 128 ? 4 : 8));
     const int NP = 32 * RPL;
-    const int TC = NP <= 128 ? 32 : 16;
+    const int TC = NP <= 64 ? 32 : 16;
     dim3 grid(n_seqs, heads, (vdim + SSM_COLS - 1) / SSM_COLS);
     TQ_REQUIRE(heads <= 65535 && grid.z <= 65535, "ssm_scan: sizes exceed the grid limit");
     const size_t smem = (size_t)(2 * TC * NP + TC * SSM_COLS + 2 * TC) * sizeof(float);
     if (RPL == 1) SSM_LAUNCH(1, 32);
     else if (RPL == 2) SSM_LAUNCH(2, 32);
-    else if (RPL == 4) SSM_LAUNCH(4, 32);
+    else if (RPL == 4) SSM_LAUNCH(4, 16);
     else SSM_LAUNCH(8, 16);
     TQ_CHECK_LAUNCH("ssm_scan");
     return 0;

@@ -48,14 +48,13 @@ def tensor_core_form(dtype: torch.dtype, kv_rank: int, rot: int) -> bool:
 
 
 def splits_for(n_tokens: int, heads: int, longest: int, device, tensor_cores: bool = False) -> int:
-    """Key ranges per token.  A block walks its range sixteen keys at a time, so a step of few tokens over long
-    ranges is cut until a block has about 64 keys (128 in the tensor-core form, which serves sixteen heads per
-    block instead of four) or the launch has three waves of blocks; prompts (many tokens) are not cut.  The ranges
-    are joined in range order, so a launch shape gives the same bits every time; logits agree across shapes to
-    rounding."""
+    """Key ranges per token.  A step of few tokens over long ranges is cut until a block has about 64 keys (the
+    CUDA-core form walks sixteen at a time, the tensor-core form, which serves sixteen heads per block instead of
+    four, 32) or the launch has three waves of blocks; prompts (many tokens) are not cut.  The ranges are joined
+    in range order, so a launch shape gives the same bits every time; logits agree across shapes to rounding."""
     blocks = n_tokens * -(-heads // (16 if tensor_cores else HEADS_PER_BLOCK))
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return int(max(1, min(64, longest // (128 if tensor_cores else 64), (3 * sms) // blocks)))
+    return int(max(1, min(64, longest // 64, (3 * sms) // blocks)))
 
 
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: torch.Tensor, sink: Optional[torch.Tensor],

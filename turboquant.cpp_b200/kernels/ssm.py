@@ -40,13 +40,13 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.
              groups: int, cu_seqlens: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
     """The recurrence over every sequence's run of new tokens.  xbc float32 [T, heads*vdim + 2*groups*n_state]
     (x | B | C after convolution and silu); the raw step sizes are proj[:, dt_off:dt_off+heads];
-    state float32 [max_slots, heads, n_state, vdim] (rows may be strided); y float32 [T, heads*vdim]."""
+    state float32 [max_slots, heads, vdim, n_state] (a head's state column by column; rows may be strided); y float32 [T, heads*vdim]."""
     for t, what in ((xbc, "x, B and C"), (proj, "the projection"), (state, "the state"), (y, "the output")):
         want_f32(t, what)
     if not (dt_bias.dtype == a_log.dtype == d_skip.dtype):
         raise KernelError("ssm_scan: the per-head constants must share a dtype")
-    if tuple(state.shape[1:]) != (heads, n_state, vdim) or not state[0].is_contiguous():
-        raise KernelError("ssm_scan: the state must be [slots, heads, state, vdim] with dense rows")
+    if tuple(state.shape[1:]) != (heads, vdim, n_state) or not state[0].is_contiguous():
+        raise KernelError("ssm_scan: the state must be [slots, heads, vdim, state] with dense rows")
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_ssm_scan(ptr(xbc), c_int(xbc.shape[1]), ptr(proj), c_int(proj.shape[1]), c_int(dt_off), ptr(dt_bias),
                                 ptr(a_log), ptr(d_skip), c_int(code(dt_bias.dtype)), ctypes_ptr(state),

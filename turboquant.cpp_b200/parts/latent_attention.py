@@ -104,14 +104,20 @@ class LatentAttentionMixer(Mixer):
         KL.latent_prepare(q, dkv, self.w_norm, self.eps, freq, mag, ctx.positions, ctx.seq_of_token, cache.page_table,
                           cache.page_size, cache.kv, H, self.dim, self.rot_dim, R)
         q3 = q.view(T, H, self.q_dim)
-        q_lat = torch.empty((T, H, R), dtype=act, device=xn.device)
+        runs = (ctx.max_q_len >= self.PROMPT_MIN_RUN and len(ctx.host_q_lens) == ctx.n_seqs
+                and len(ctx.host_seq_start) == ctx.n_seqs)
+        # the prompt path wants [query in the latent space | rotated part] side by side: the product writes there
+        qa = torch.empty((T, H, R + self.rot_dim), dtype=act, device=xn.device) if runs else None
+        q_lat = qa[:, :, :R] if runs else torch.empty((T, H, R), dtype=act, device=xn.device)
         if self.dim:
             batched_linear(q3[:, :, :self.dim].transpose(0, 1), self.w_uk, q_lat.transpose(0, 1))
         else:
             q_lat.zero_()
         sums = torch.empty((T, H, R), dtype=act, device=xn.device)
-        if ctx.max_q_len >= self.PROMPT_MIN_RUN and len(ctx.host_q_lens) == ctx.n_seqs and len(ctx.host_seq_start) == ctx.n_seqs:
-            self._attend_runs(q3, q_lat, sums, ctx, cache)
+        if runs:
+            if self.rot_dim:
+                qa[:, :, R:].copy_(q3[:, :, self.dim:])
+            self._attend_runs(qa, sums, ctx, cache)
         else:
             self._attend_tokens(q, q_lat, sums, ctx, cache)
         v = torch.empty((T, H, self.vdim), dtype=act, device=xn.device)
@@ -128,14 +134,14 @@ class LatentAttentionMixer(Mixer):
         KL.latent_attention(q_lat, q, self.dim, cache.kv, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                             cache.page_size, self.window, self.scale, sums, H, R, self.rot_dim, n_splits, partial)
 
-    def _attend_runs(self, q3, q_lat, sums, ctx: StepContext, cache: LayerCache) -> None:
+    def _attend_runs(self, qa, sums, ctx: StepContext, cache: LayerCache) -> None:
         """Long runs of new tokens (prompts): all heads of a block of tokens meet the same cached rows, so scores
         and weighted sums are two matrix products of the library over (token, head) rows, with the mask, the
         scale and the softmax with its sink between them in a kernel of their own (float32 scores in, weights in
         the activation dtype out).  A block's rows are gathered from the pages once.  It walks the step's
         sequences on the host; steps of single tokens never come here."""
         H, R, Dk = self.heads, self.kv_rank, self.kv_rank + self.rot_dim
-        act, dev = q_lat.dtype, q_lat.device
+        act, dev = qa.dtype, qa.device
         block = max(16, self.PROMPT_ROWS // H)
         t0 = 0
         for i, (n, start) in enumerate(zip(ctx.host_q_lens, ctx.host_seq_start)):
@@ -151,11 +157,7 @@ class LatentAttentionMixer(Mixer):
                 KL.latent_gather(cache.kv, cache.page_table[i], cache.page_size, k0, n_keys, rows[:n_keys])
                 if n_pad > n_keys:
                     rows[n_keys:].zero_()
-                qa = torch.empty((b - a, H, Dk), dtype=act, device=dev)            # [query in the latent space | rotated part]
-                qa[:, :, :R].copy_(q_lat[t0 + a:t0 + b])
-                if self.rot_dim:
-                    qa[:, :, R:].copy_(q3[t0 + a:t0 + b, :, self.dim:])
-                scores = product(qa.view(-1, Dk), rows.t(), out_dtype=torch.float32)
+                scores = product(qa[t0 + a:t0 + b].view(-1, Dk), rows.t(), out_dtype=torch.float32)
                 weights = torch.empty(scores.shape, dtype=act, device=dev)
                 KL.latent_softmax(scores, self.sink, self.scale, self.window, pos0, k0, H, weights)
                 product(weights, rows[:, :R], out=sums[t0 + a:t0 + b].view(-1, R))

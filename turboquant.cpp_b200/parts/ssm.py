@@ -9,8 +9,8 @@ zeros before a sequence's start) and silu.  Per head a (using group a // (heads 
     y   = S^T C + D_a x
 
 then y * silu(z), an RMS norm in `norm_groups` equal parts with a weight, and the output projection.  A sequence's
-state is S of every head and the convolution's last taps-1 inputs, both float32, in one row of the cache's state
-area.  The projection leaves the library's product as float32 and everything up to the gated norm stays float32.
+state is S of every head (stored column by column, [vdim, N]) and the convolution's last taps-1 inputs, both
+float32, in one row of the cache's state area.  The projection leaves the library's product as float32 and everything up to the gated norm stays float32.
 """
 from __future__ import annotations
 
@@ -73,7 +73,7 @@ class Mamba2Mixer(Mixer):
         T, dev = xn.shape[0], xn.device
         st = cache.state                                                       # [max_slots, kept | S]
         kept = st[:, :self.kept_size].unflatten(1, (self.taps - 1, self.channels))
-        S = st[:, self.kept_size:].unflatten(1, (self.heads, self.n_state, self.vdim))
+        S = st[:, self.kept_size:].unflatten(1, (self.heads, self.vdim, self.n_state))     # column by column
         proj = linear(xn, self.w_in, out_dtype=torch.float32)                  # [T, z | x | B | C | dt]
         xbc = torch.empty((T, self.channels), dtype=torch.float32, device=dev)
         KS.conv_silu(proj, self.inner, self.w_conv, self.b_conv, kept, xbc, ctx.seq_of_token, ctx.cu_seqlens, ctx.slots)
