@@ -317,24 +317,19 @@ __device__ __forceinline__ uint32_t lat_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
-__device__ __forceinline__ void lat_ldsm4(uint32_t* r, const void* p) {
+// ldmatrix from a shared-memory address (32 bits, bytes)
+__device__ __forceinline__ void lat_ldsm4(uint32_t* r, unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
 }
-__device__ __forceinline__ void lat_ldsm2(uint32_t* r, const void* p) {
+__device__ __forceinline__ void lat_ldsm2(uint32_t* r, unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-                 : "=r"(r[0]), "=r"(r[1]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(a) : "memory");
 }
-__device__ __forceinline__ void lat_ldsm4_t(uint32_t* r, const void* p) {
+__device__ __forceinline__ void lat_ldsm4_t(uint32_t* r, unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
 }
-// 16 bytes global -> shared, or 16 zero bytes when `bytes` is 0 (the source is not read then)
-__device__ __forceinline__ void lat_cp16(void* dst, const void* src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                 ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
-}
-
 template <int OT>      // output n-tiles (of 8 columns) per warp: R = 32 * OT
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q, int q_dim,
@@ -361,21 +356,33 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
 
     // a tile's rows go round the warps; a lane copies every 32nd piece of a row (rows beyond the range as zeros)
-    auto fetch = [&](int p0, __nv_bfloat16* dst) {
-        for (int r = warp; r < LATM_KEYS; r += LAT_WARPS) {
-            const int p = p0 + r;
-            const __nv_bfloat16* src = cache;
-            int bytes = 0;
+    // a tile's rows go round the warps (row r to warp r % 4); lanes 0..7 each find one of the warp's eight rows in
+    // the pages, the others get the place by shuffle; a lane copies every 32nd piece of a row (rows beyond the
+    // range as zeros)
+    const unsigned ks_s = (unsigned)__cvta_generic_to_shared(Ks);
+    auto fetch = [&](int p0, int stage) {
+        long long mine = -1;
+        {
+            const int p = p0 + warp + LAT_WARPS * (lane & 7);
             if (p < hi) {
                 const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
-                src = cache + ((size_t)page * page_size + p % page_size) * Dk;
-                bytes = 16;
+                mine = ((long long)page * page_size + p % page_size) * Dk;
             }
-            for (int c = lane; c < chunks; c += 32) lat_cp16(dst + r * ld + 8 * c, bytes ? src + 8 * c : src, bytes);
+        }
+        const unsigned dst = ks_s + (unsigned)(stage * LATM_KEYS * ld) * 2u;
+#pragma unroll
+        for (int i = 0; i < LATM_KEYS / LAT_WARPS; ++i) {
+            const long long off = __shfl_sync(0xffffffffu, mine, i);
+            const int r = warp + LAT_WARPS * i;
+            const __nv_bfloat16* src = cache + (off < 0 ? 0 : off);
+            const int bytes = off < 0 ? 0 : 16;
+            for (int c = lane; c < chunks; c += 32)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                             ::"r"(dst + (unsigned)(r * ld + 8 * c) * 2u), "l"(src + (bytes ? 8 * c : 0)), "r"(bytes) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (lo < hi) fetch(lo, Ks);
+    if (lo < hi) fetch(lo, 0);
     {   // the heads' queries, 16 bytes at a time (heads beyond H as zeros)
         const int rc = rot / 8, lc = R / 8;
         const bool rot_vec = (q_dim % 8 == 0) && (q_off % 8 == 0);
@@ -407,41 +414,59 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     const int col_base = warp * OT * 8;
     // ldmatrix addresses: the queries' 16 x 16 piece (lane i: row i % 16, second eight columns for i >= 16), this
     // warp's eight keys (lane i: key i % 8, columns 8 * (i / 8) on), a tile's 32 rows as values (lane i: row i)
-    const __nv_bfloat16* qa = Qs + (lane & 15) * ld + 8 * (lane >> 4);
-    const int kb_off = (8 * warp + (lane & 7)) * ld + 8 * (lane >> 3);
+    const unsigned qa = (unsigned)__cvta_generic_to_shared(Qs + (lane & 15) * ld + 8 * (lane >> 4));
+    const unsigned kb_off = (unsigned)((8 * warp + (lane & 7)) * ld + 8 * (lane >> 3)) * 2u;
+    const unsigned va_off = (unsigned)(lane * ld + warp * OT * 8) * 2u;
     const int ksteps = Dk / 16;
+    const float scale2 = scale * 1.4426950408889634f;           // scores in units of ln 2: the exponentials are exp2
 
     int stage = 0;
     for (int p0 = lo; p0 < hi; p0 += LATM_KEYS, stage ^= 1) {
-        const __nv_bfloat16* Kt = Ks + stage * LATM_KEYS * ld;
+        const unsigned kt = ks_s + (unsigned)(stage * LATM_KEYS * ld) * 2u;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                          // the tile has landed for all; the other stage and Ps are free
-        if (p0 + LATM_KEYS < hi) fetch(p0 + LATM_KEYS, Ks + (stage ^ 1) * LATM_KEYS * ld);
-        // scores of this warp's eight keys: two chains of accumulators, joined at the end
+        if (p0 + LATM_KEYS < hi) fetch(p0 + LATM_KEYS, stage ^ 1);
+        // scores of this warp's eight keys: four chains of accumulators, joined at the end
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        float sc4[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
         int ks = 0;
+        for (; ks + 4 <= ksteps; ks += 4) {
+            uint32_t a0[4], a1[4], a2[4], a3[4], b0[4], b1[4];
+            lat_ldsm4(a0, qa + 32 * ks);
+            lat_ldsm4(a1, qa + 32 * ks + 32);
+            lat_ldsm4(a2, qa + 32 * ks + 64);
+            lat_ldsm4(a3, qa + 32 * ks + 96);
+            lat_ldsm4(b0, kt + kb_off + 32 * ks);
+            lat_ldsm4(b1, kt + kb_off + 32 * ks + 64);
+            lat_mma16816(sa, a0, b0[0], b0[1]);
+            lat_mma16816(sb, a1, b0[2], b0[3]);
+            lat_mma16816(sc4, a2, b1[0], b1[1]);
+            lat_mma16816(sd, a3, b1[2], b1[3]);
+        }
         for (; ks + 2 <= ksteps; ks += 2) {
             uint32_t a0[4], a1[4], b[4];
-            lat_ldsm4(a0, qa + 16 * ks);
-            lat_ldsm4(a1, qa + 16 * ks + 16);
-            lat_ldsm4(b, Kt + kb_off + 16 * ks);
+            lat_ldsm4(a0, qa + 32 * ks);
+            lat_ldsm4(a1, qa + 32 * ks + 32);
+            lat_ldsm4(b, kt + kb_off + 32 * ks);
             lat_mma16816(sa, a0, b[0], b[1]);
             lat_mma16816(sb, a1, b[2], b[3]);
         }
         if (ks < ksteps) {
             uint32_t a0[4], b[2];
-            lat_ldsm4(a0, qa + 16 * ks);
-            lat_ldsm2(b, Kt + kb_off + 16 * ks);      // lanes 0..15 give the addresses: columns 16 ks and 16 ks + 8
+            lat_ldsm4(a0, qa + 32 * ks);
+            lat_ldsm2(b, kt + kb_off + 32 * ks);      // lanes 0..15 give the addresses: columns 16 ks and 16 ks + 8
             lat_mma16816(sa, a0, b[0], b[1]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sa[i] = (sa[i] + sb[i]) + (sc4[i] + sd[i]);
         {   // this lane holds keys 8 warp + 2 tq + {0, 1} of rows g (values 0, 1) and g + 8 (values 2, 3)
             const int kc = 8 * warp + 2 * tq;
             const bool s0 = p0 + kc < hi, s1 = p0 + kc + 1 < hi;
             float2 top, bot;
-            top.x = s0 ? (sa[0] + sb[0]) * scale : -INFINITY;
-            top.y = s1 ? (sa[1] + sb[1]) * scale : -INFINITY;
-            bot.x = s0 ? (sa[2] + sb[2]) * scale : -INFINITY;
-            bot.y = s1 ? (sa[3] + sb[3]) * scale : -INFINITY;
+            top.x = s0 ? sa[0] * scale2 : -INFINITY;
+            top.y = s1 ? sa[1] * scale2 : -INFINITY;
+            bot.x = s0 ? sa[2] * scale2 : -INFINITY;
+            bot.y = s1 ? sa[3] * scale2 : -INFINITY;
             *reinterpret_cast<float2*>(Ps + g * LATM_PS + kc) = top;
             *reinterpret_cast<float2*>(Ps + (g + 8) * LATM_PS + kc) = bot;
         }
@@ -466,12 +491,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
             tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
             const float m_new = fmaxf(m[r], tmax);             // finite: a tile has at least one key
-            corr[r] = expf(m[r] - m_new);                       // exp(-inf) = 0 on the first tile
+            corr[r] = exp2f(m[r] - m_new);                      // 2^(-inf) = 0 on the first tile
             m[r] = m_new;
             l[r] *= corr[r];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                sc[r][i] = expf(sc[r][i] - m_new);
+                sc[r][i] = exp2f(sc[r][i] - m_new);
                 l[r] += sc[r][i];                               // this lane's share; the quad's shares are added at the end
             }
         }
@@ -483,12 +508,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
             pa[k2][2] = lat_pack(sc[0][4 * k2 + 2], sc[0][4 * k2 + 3]);
             pa[k2][3] = lat_pack(sc[1][4 * k2 + 2], sc[1][4 * k2 + 3]);
         }
-        const __nv_bfloat16* va = Kt + lane * ld + col_base;
 #pragma unroll
         for (int j = 0; j < OT; ++j) {
             o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
             uint32_t b[4];
-            lat_ldsm4_t(b, va + 8 * j);
+            lat_ldsm4_t(b, kt + va_off + 16 * j);
             lat_mma16816(o[j], pa[0], b[0], b[1]);
             lat_mma16816(o[j], pa[1], b[2], b[3]);
         }
@@ -497,6 +521,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     for (int r = 0; r < 2; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        m[r] *= 0.6931471805599453f;                            // back to natural units for the sink and the merge
     }
     const bool whole = gridDim.z == 1;
 #pragma unroll
@@ -524,8 +549,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
 
 // joins the ranges of one (token, head) in range order and lets the sink take part: the first warp turns the
 // ranges' maxima and sums into one weight per range (the sink only adds to the denominator), then every thread
-// adds up its elements over the ranges
+// adds up one element over the ranges; grid (tokens, heads, ceil(R / LAT_MERGE_THREADS))
 #define LAT_MAX_SPLITS 64
+#define LAT_MERGE_THREADS 128
 template <typename TA>
 __global__ void latent_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, int n_splits,
                                     int H, int R, TA* __restrict__ out) {
@@ -557,12 +583,12 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, const flo
         for (int i = 0; i < LAT_MAX_SPLITS / 32; ++i) wgt[lane + 32 * i] = ms[i] / L;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < R; e += blockDim.x) {
-        float v = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < n_splits; ++s) v += pp[(size_t)s * (R + 2) + 2 + e] * wgt[s];
-        out[((size_t)t * H + h) * R + e] = tq_from_float<TA>(v);
-    }
+    const int e = blockIdx.z * LAT_MERGE_THREADS + threadIdx.x;
+    if (e >= R) return;
+    float v = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) v += pp[(size_t)s * (R + 2) + 2 + e] * wgt[s];
+    out[((size_t)t * H + h) * R + e] = tq_from_float<TA>(v);
 }
 
 // TQ_LATENT_NO_MMA=1: the CUDA-core form for bfloat16 too
@@ -631,10 +657,10 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
     }
     TQ_CHECK_LAUNCH("latent_attention");
     if (n_splits > 1) {
-        dim3 mgrid(T_, H);
+        dim3 mgrid(T_, H, (R + LAT_MERGE_THREADS - 1) / LAT_MERGE_THREADS);
         TQ_REQUIRE(H <= 65535, "latent_attention: %d heads exceed the grid limit", H);
         TQ_DISPATCH(act_dtype, TA,
-            (tq_launch(mgrid, 128, 0, stream)(latent_merge_kernel<TA>, (const float*)partial, sink, n_splits, H, R, (TA*)out)));
+            (tq_launch(mgrid, LAT_MERGE_THREADS, 0, stream)(latent_merge_kernel<TA>, (const float*)partial, sink, n_splits, H, R, (TA*)out)));
         TQ_CHECK_LAUNCH("latent_merge");
     }
     return 0;

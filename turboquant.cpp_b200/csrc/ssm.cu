@@ -109,29 +109,30 @@ TQ_EXPORT int tq_conv_silu(const float* proj, int P, int off, const void* w, con
 }
 
 // ---------------------------------------------------------------------------------------
-// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_WARPS warps per block.  A warp owns SSM_CPW
-// neighbouring columns of the head's state (kept column by column, [vdim][N], so the lanes' loads and stores are
-// neighbours in memory): lane l keeps rows l, l+32, ... (RPL of them) of each column in registers for the whole run, so a step reads its B and C values once for the four columns and does RPL x 4
-// multiply-adds for the state and as many for y.  The sums of y over the lanes are not taken step by step: eight
-// steps leave 32 partial sums per lane, which five rounds of exchanges (31 shuffles) turn into one whole sum per
-// lane, so the chain of dependent shuffles is paid once per eight steps and the state's updates run on
-// meanwhile.  No barrier between steps.  The run is walked in chunks of TC steps whose B, C, x, step sizes and
-// decays lie in shared memory (rows beyond N as zeros, so the state's padding rows stay zero and need no test); a
-// chunk's inputs are fetched into registers, all loads in flight together, while the chunk before is computed.
+// ssm_scan: grid (sequences, heads, ceil(vdim / SSM_COLS)), SSM_COLS / SSM_CPW warps per block.  A warp owns
+// SSM_CPW neighbouring columns of the head's state (kept column by column, [vdim][N], so the lanes' loads and
+// stores are neighbours in memory): lane l keeps rows l, l+32, ... (RPL of them) of each column in registers for
+// the whole run, so a step reads its B and C values once for the warp's columns and does three float32 operations
+// per element of the state (the product B x, the decayed sum, the sum for y).  The sums of y over the lanes are
+// not taken step by step: 32 / SSM_CPW steps leave 32 partial sums per lane, which five rounds of exchanges (31
+// shuffles) turn into one whole sum per lane, so the chain of dependent shuffles is paid once per group of steps
+// and the state's updates run on meanwhile; a whole group is straight-line code.  No barrier between steps.  The
+// run is walked in chunks of TC steps whose B, C, x, step sizes and decays lie in shared memory (rows beyond N as
+// zeros, so the state's padding rows stay zero and need no test); a chunk's inputs are fetched into registers,
+// all loads in flight together, while the chunk before is computed.
 // ---------------------------------------------------------------------------------------
-#define SSM_WARPS 8
-#define SSM_CPW 4
-#define SSM_COLS (SSM_WARPS * SSM_CPW)
-#define SSM_GROUP 8           // steps whose sums over the lanes are taken together; SSM_GROUP * SSM_CPW is a warp's 32 lanes
+#define SSM_COLS 32           // columns of the state per block
 
-template <typename TW, int RPL, int TC>
-__global__ void __launch_bounds__(32 * SSM_WARPS)
+// SSM_CPW columns per warp (4 or 2), SSM_COLS / SSM_CPW warps, 32 / SSM_CPW steps whose sums are taken together
+template <typename TW, int RPL, int TC, int SSM_CPW>
+__global__ void __launch_bounds__(32 * SSM_COLS / SSM_CPW)
 ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ proj, int P, int dt_off,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, long long slot_stride, float* __restrict__ y, int heads, int vdim, int N,
                 int groups, const int* __restrict__ cu_seqlens, const int* __restrict__ slots) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int SSM_WARPS = SSM_COLS / SSM_CPW, SSM_GROUP = 32 / SSM_CPW;
     extern __shared__ float4 ssm_smem4[];
     float* ssm_smem = reinterpret_cast<float*>(ssm_smem4);
     constexpr int NP = 32 * RPL;             // rows with padding
@@ -208,8 +209,14 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
 #pragma unroll
                     for (int c = 0; c < SSM_CPW; ++c) v[j * SSM_CPW + c] = 0.f;
                     if (decltype(full)::value || tt < tc) {          // the same for the whole block
-                        const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * SSM_COLS + warp * SSM_CPW);
-                        const float xv[SSM_CPW] = {x4.x, x4.y, x4.z, x4.w};
+                        float xv[SSM_CPW];
+                        if constexpr (SSM_CPW == 4) {
+                            const float4 x4 = *reinterpret_cast<const float4*>(xs + tt * SSM_COLS + warp * SSM_CPW);
+                            xv[0] = x4.x; xv[1] = x4.y; xv[2] = x4.z; xv[3] = x4.w;
+                        } else {
+                            const float2 x2 = *reinterpret_cast<const float2*>(xs + tt * SSM_COLS + warp * SSM_CPW);
+                            xv[0] = x2.x; xv[1] = x2.y;
+                        }
                         const float a = dec[tt], dt = dts[tt];
 #pragma unroll
                         for (int r = 0; r < RPL; ++r) {
@@ -236,7 +243,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
                     v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
                 }
             }
-            const int tt = t8 + (lane >> 2), c = lane & 3;          // SSM_GROUP * SSM_CPW == 32
+            const int tt = t8 + lane / SSM_CPW, c = lane % SSM_CPW;   // SSM_GROUP * SSM_CPW == 32
             if (tt < tc && vw + c < vdim)
                 y[(size_t)(first + t0 + tt) * inner + (size_t)h * vdim + vw + c] =
                     v[0] + D * xs[tt * SSM_COLS + warp * SSM_CPW + c];
@@ -253,11 +260,17 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, const float* __restrict__ 
     }
 }
 
-#define SSM_LAUNCH(RPL_, TC_)                                                                                     \
+#define SSM_LAUNCH(RPL_, TC_, CPW_)                                                                               \
     TQ_DISPATCH(w_dtype, TW,                                                                                      \
-        (tq_launch(grid, 32 * SSM_WARPS, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_>, xbc, C, proj, P, dt_off,    \
+        (tq_launch(grid, 32 * SSM_COLS / CPW_, smem, stream)(ssm_scan_kernel<TW, RPL_, TC_, CPW_>, xbc, C, proj, P, dt_off, \
             (const TW*)dt_bias, (const TW*)a_log, (const TW*)d_skip, state, slot_stride, y, heads, vdim, N, groups, \
             cu_seqlens, slots)))
+
+// TQ_SSM_CPW=2: sixteen warps of two columns instead of eight of four (measured slower at every size tried)
+static int ssm_cpw() {
+    static const int v = [] { const char* e = getenv("TQ_SSM_CPW"); return e && e[0] == '2' ? 2 : 4; }();
+    return v;
+}
 
 TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int dt_off, const void* dt_bias,
                           const void* a_log, const void* d_skip, int w_dtype, float* state, long long slot_stride,
@@ -274,10 +287,17 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
     dim3 grid(n_seqs, heads, (vdim + SSM_COLS - 1) / SSM_COLS);
     TQ_REQUIRE(heads <= 65535 && grid.z <= 65535, "ssm_scan: sizes exceed the grid limit");
     const size_t smem = (size_t)(2 * TC * NP + TC * SSM_COLS + 2 * TC) * sizeof(float);
-    if (RPL == 1) SSM_LAUNCH(1, 32);
-    else if (RPL == 2) SSM_LAUNCH(2, 32);
-    else if (RPL == 4) SSM_LAUNCH(4, 16);
-    else SSM_LAUNCH(8, 16);
+    if (ssm_cpw() == 4) {
+        if (RPL == 1) SSM_LAUNCH(1, 32, 4);
+        else if (RPL == 2) SSM_LAUNCH(2, 32, 4);
+        else if (RPL == 4) SSM_LAUNCH(4, 16, 4);
+        else SSM_LAUNCH(8, 16, 4);
+    } else {
+        if (RPL == 1) SSM_LAUNCH(1, 32, 2);
+        else if (RPL == 2) SSM_LAUNCH(2, 32, 2);
+        else if (RPL == 4) SSM_LAUNCH(4, 16, 2);
+        else SSM_LAUNCH(8, 16, 2);
+    }
     TQ_CHECK_LAUNCH("ssm_scan");
     return 0;
 }

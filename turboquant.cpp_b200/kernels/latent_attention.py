@@ -48,13 +48,16 @@ def tensor_core_form(dtype: torch.dtype, kv_rank: int, rot: int) -> bool:
 
 
 def splits_for(n_tokens: int, heads: int, longest: int, device, tensor_cores: bool = False) -> int:
-    """Key ranges per token.  A step of few tokens over long ranges is cut until a block has about 64 keys (the
-    CUDA-core form walks sixteen at a time, the tensor-core form, which serves sixteen heads per block instead of
-    four, 32) or the launch has three waves of blocks; prompts (many tokens) are not cut.  The ranges are joined
-    in range order, so a launch shape gives the same bits every time; logits agree across shapes to rounding."""
+    """Key ranges per token.  A step of few tokens over long ranges is cut until a block has about 64 keys or the
+    launch fills the GPU: three waves of blocks in the CUDA-core form (four heads a block, sixteen keys at a time),
+    one wave of two blocks per SM in the tensor-core form (sixteen heads a block, tiles of 32 keys, two blocks'
+    shared memory per SM), whose blocks are long enough for a second, partly filled wave to cost more than it
+    brings.  Prompts (many tokens) are not cut.  The ranges are joined in range order, so a launch shape gives the
+    same bits every time; logits agree across shapes to rounding."""
     blocks = n_tokens * -(-heads // (16 if tensor_cores else HEADS_PER_BLOCK))
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return int(max(1, min(64, longest // 64, (3 * sms) // blocks)))
+    room = (2 * sms) // blocks if tensor_cores else (3 * sms) // blocks
+    return int(max(1, min(64, longest // 64, room)))
 
 
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_off: int, cache: torch.Tensor, sink: Optional[torch.Tensor],
