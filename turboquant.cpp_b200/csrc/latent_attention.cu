@@ -40,9 +40,18 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, const float* __restric
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float scratch[33];
+    __shared__ float s_cos[LAT_MAX_ROW / 2], s_sin[LAT_MAX_ROW / 2];
     const int t = blockIdx.x;
     const int pos = positions[t];
     const float fpos = (float)pos;
+    // the token's cos and sin once (times mag), for the key part and for every head
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        float s, c;
+        sincosf(fpos * freq[i], &s, &c);
+        s_cos[i] = c * mag;
+        s_sin[i] = s * mag;
+    }
+    __syncthreads();
     if (dkv) {
         const float* d = dkv + (size_t)t * (R + rot);
         float ss = 0.f;
@@ -55,9 +64,7 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, const float* __restric
         TA* row = cache + ((size_t)page * page_size + pos % page_size) * (R + rot);
         for (int i = threadIdx.x; i < R; i += blockDim.x) row[i] = tq_from_float<TA>(d[i] * rs * tq_to_float(wnorm[i]));
         for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-            float s, c;
-            sincosf(fpos * freq[i], &s, &c);
-            s *= mag; c *= mag;
+            const float s = s_sin[i], c = s_cos[i];
             const float u = d[R + 2 * i], v = d[R + 2 * i + 1];
             row[R + 2 * i] = tq_from_float<TA>(u * c - v * s);
             row[R + 2 * i + 1] = tq_from_float<TA>(v * c + u * s);
@@ -66,9 +73,7 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, const float* __restric
     }
     for (int k = threadIdx.x; k < heads * n_pairs; k += blockDim.x) {
         const int h = k / n_pairs, i = k % n_pairs;
-        float s, c;
-        sincosf(fpos * freq[i], &s, &c);
-        s *= mag; c *= mag;
+        const float s = s_sin[i], c = s_cos[i];
         TA* p = q + ((size_t)t * heads + h) * q_dim + q_off + 2 * i;
         const float u = tq_to_float(p[0]), v = tq_to_float(p[1]);
         p[0] = tq_from_float<TA>(u * c - v * s);
