@@ -301,11 +301,12 @@ latent_attention_kernel(const TA* __restrict__ q_lat, const TA* __restrict__ q, 
 // The same on tensor cores (bfloat16, R a multiple of 32 up to 512, R + rot a multiple of 16): the block's sixteen
 // heads are the sixteen rows of mma.sync m16n8k16, so one cached row serves sixteen dot products per
 // instruction.  Keys come in tiles of 32 through a two-stage ring in shared memory, filled by 16-byte cp.async
-// copies a tile ahead.  Of a tile's scores (16 heads x 32 keys) every warp computes the eight keys that are its
-// own (fp32 accumulators; scale and mask on the fragments) and leaves them in shared memory; after a barrier
+// copies a tile ahead.  Of a tile's scores (16 heads x 32 keys) every warp computes a group of eight keys (with
+// eight warps, where R is a multiple of 64, half of the row's elements for it; fp32 accumulators; scale and mask
+// on the fragments) and leaves them in shared memory; after a barrier
 // every warp reads all of them, keeps the online softmax of its two rows (all warps the same numbers) and
 // multiplies the weights, rounded to bfloat16 as the second operand's type demands, with the tile's rows for the
-// quarter of the R output columns that it owns.  Fragments come from shared memory by ldmatrix (transposed for
+// share of the R output columns that it owns.  Fragments come from shared memory by ldmatrix (transposed for
 // the rows as values).
 // ---------------------------------------------------------------------------------------
 #define LATM_HEADS 16
@@ -335,8 +336,10 @@ __device__ __forceinline__ void lat_ldsm4_t(uint32_t* r, unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a) : "memory");
 }
-template <int OT>      // output n-tiles (of 8 columns) per warp: R = 32 * OT
-__global__ void __launch_bounds__(LAT_WARPS * 32)
+// NW warps (4 or 8); OT output n-tiles (of 8 columns) per warp: R = 8 * NW * OT.  With eight warps two warps share a
+// group of eight keys, each taking half of the row's elements, and their partial scores meet in shared memory.
+template <int OT, int NW>
+__global__ void __launch_bounds__(NW * 32, 2)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q, int q_dim,
                             int q_off, const __nv_bfloat16* __restrict__ cache, const float* __restrict__ sink,
                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -349,7 +352,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     const int Dk = R + rot, ld = Dk + LATM_PAD;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(latm_smem);       // [16 heads][ld]
     __nv_bfloat16* Ks = Qs + LATM_HEADS * ld;                               // [2][32 keys][ld]
-    float* Ps = reinterpret_cast<float*>(Ks + 2 * LATM_KEYS * ld);          // [16 heads][LATM_PS]
+    float* Ps = reinterpret_cast<float*>(Ks + 2 * LATM_KEYS * ld);          // [NW / 4][16 heads][LATM_PS]
     const int t = blockIdx.x, h0 = blockIdx.y * LATM_HEADS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tq = lane & 3;
     const int chunks = Dk / 8;                                              // 16-byte pieces of a row
@@ -361,14 +364,14 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
 
     // a tile's rows go round the warps; a lane copies every 32nd piece of a row (rows beyond the range as zeros)
-    // a tile's rows go round the warps (row r to warp r % 4); lanes 0..7 each find one of the warp's eight rows in
+    // a tile's rows go round the warps (row r to warp r % NW); the first lanes each find one of the warp's rows in
     // the pages, the others get the place by shuffle; a lane copies every 32nd piece of a row (rows beyond the
     // range as zeros)
     const unsigned ks_s = (unsigned)__cvta_generic_to_shared(Ks);
     auto fetch = [&](int p0, int stage) {
         long long mine = -1;
         {
-            const int p = p0 + warp + LAT_WARPS * (lane & 7);
+            const int p = p0 + warp + NW * (lane % (LATM_KEYS / NW));
             if (p < hi) {
                 const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
                 mine = ((long long)page * page_size + p % page_size) * Dk;
@@ -376,9 +379,9 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
         }
         const unsigned dst = ks_s + (unsigned)(stage * LATM_KEYS * ld) * 2u;
 #pragma unroll
-        for (int i = 0; i < LATM_KEYS / LAT_WARPS; ++i) {
+        for (int i = 0; i < LATM_KEYS / NW; ++i) {
             const long long off = __shfl_sync(0xffffffffu, mine, i);
-            const int r = warp + LAT_WARPS * i;
+            const int r = warp + NW * i;
             const __nv_bfloat16* src = cache + (off < 0 ? 0 : off);
             const int bytes = off < 0 ? 0 : 16;
             for (int c = lane; c < chunks; c += 32)
@@ -420,9 +423,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
     // ldmatrix addresses: the queries' 16 x 16 piece (lane i: row i % 16, second eight columns for i >= 16), this
     // warp's eight keys (lane i: key i % 8, columns 8 * (i / 8) on), a tile's 32 rows as values (lane i: row i)
     const unsigned qa = (unsigned)__cvta_generic_to_shared(Qs + (lane & 15) * ld + 8 * (lane >> 4));
-    const unsigned kb_off = (unsigned)((8 * warp + (lane & 7)) * ld + 8 * (lane >> 3)) * 2u;
+    const int nt = warp & 3, kp = warp >> 2;                   // the warp's group of eight keys; its part of the row (NW == 8)
+    const unsigned kb_off = (unsigned)((8 * nt + (lane & 7)) * ld + 8 * (lane >> 3)) * 2u;
     const unsigned va_off = (unsigned)(lane * ld + warp * OT * 8) * 2u;
     const int ksteps = Dk / 16;
+    const int ks_mid = NW == 8 ? ((ksteps / 2 + 1) & ~1) : ksteps;           // an even number of steps to the first part
+    const int ks_lo = kp ? ks_mid : 0, ks_hi = kp ? ksteps : ks_mid;
     const float scale2 = scale * 1.4426950408889634f;           // scores in units of ln 2: the exponentials are exp2
 
     int stage = 0;
@@ -434,8 +440,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
         // scores of this warp's eight keys: four chains of accumulators, joined at the end
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
         float sc4[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
-        int ks = 0;
-        for (; ks + 4 <= ksteps; ks += 4) {
+        int ks = ks_lo;
+        for (; ks + 4 <= ks_hi; ks += 4) {
             uint32_t a0[4], a1[4], a2[4], a3[4], b0[4], b1[4];
             lat_ldsm4(a0, qa + 32 * ks);
             lat_ldsm4(a1, qa + 32 * ks + 32);
@@ -448,7 +454,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
             lat_mma16816(sc4, a2, b1[0], b1[1]);
             lat_mma16816(sd, a3, b1[2], b1[3]);
         }
-        for (; ks + 2 <= ksteps; ks += 2) {
+        for (; ks + 2 <= ks_hi; ks += 2) {
             uint32_t a0[4], a1[4], b[4];
             lat_ldsm4(a0, qa + 32 * ks);
             lat_ldsm4(a1, qa + 32 * ks + 32);
@@ -456,7 +462,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
             lat_mma16816(sa, a0, b[0], b[1]);
             lat_mma16816(sb, a1, b[2], b[3]);
         }
-        if (ks < ksteps) {
+        if (ks < ks_hi) {
             uint32_t a0[4], b[2];
             lat_ldsm4(a0, qa + 32 * ks);
             lat_ldsm2(b, kt + kb_off + 32 * ks);      // lanes 0..15 give the addresses: columns 16 ks and 16 ks + 8
@@ -464,16 +470,17 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) sa[i] = (sa[i] + sb[i]) + (sc4[i] + sd[i]);
-        {   // this lane holds keys 8 warp + 2 tq + {0, 1} of rows g (values 0, 1) and g + 8 (values 2, 3)
-            const int kc = 8 * warp + 2 * tq;
+        {   // this lane holds keys 8 nt + 2 tq + {0, 1} of rows g (values 0, 1) and g + 8 (values 2, 3)
+            const int kc = 8 * nt + 2 * tq;
             const bool s0 = p0 + kc < hi, s1 = p0 + kc + 1 < hi;
             float2 top, bot;
             top.x = s0 ? sa[0] * scale2 : -INFINITY;
             top.y = s1 ? sa[1] * scale2 : -INFINITY;
             bot.x = s0 ? sa[2] * scale2 : -INFINITY;
             bot.y = s1 ? sa[3] * scale2 : -INFINITY;
-            *reinterpret_cast<float2*>(Ps + g * LATM_PS + kc) = top;
-            *reinterpret_cast<float2*>(Ps + (g + 8) * LATM_PS + kc) = bot;
+            float* pw = Ps + kp * LATM_HEADS * LATM_PS;
+            *reinterpret_cast<float2*>(pw + g * LATM_PS + kc) = top;
+            *reinterpret_cast<float2*>(pw + (g + 8) * LATM_PS + kc) = bot;
         }
         __syncthreads();
         // all 32 scores of rows g and g + 8, in the first operand's layout: sc[r][2 i + {0, 1}] = keys 8 i + 2 tq + {0, 1}
@@ -482,7 +489,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_lat, const __nv_
         for (int r = 0; r < 2; ++r) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float2 v = *reinterpret_cast<const float2*>(Ps + (g + 8 * r) * LATM_PS + 8 * i + 2 * tq);
+                float2 v = *reinterpret_cast<const float2*>(Ps + (g + 8 * r) * LATM_PS + 8 * i + 2 * tq);
+                if (NW == 8) {                      // the other part of the row (masked keys are -inf in both)
+                    const float2 u = *reinterpret_cast<const float2*>(Ps + (LATM_HEADS + g + 8 * r) * LATM_PS + 8 * i + 2 * tq);
+                    v.x += u.x;
+                    v.y += u.y;
+                }
                 sc[r][2 * i] = v.x;
                 sc[r][2 * i + 1] = v.y;
             }
@@ -628,26 +640,43 @@ TQ_EXPORT int tq_latent_attention(const void* q_lat, const void* q, int q_dim, i
         dim3 grid(T_, (H + LATM_HEADS - 1) / LATM_HEADS, n_splits);
         TQ_REQUIRE(grid.y <= 65535, "latent_attention: %d heads exceed the grid limit", H);
         const size_t smem = (size_t)(LATM_HEADS + 2 * LATM_KEYS) * (Dk + LATM_PAD) * sizeof(__nv_bfloat16) +
-                            (size_t)LATM_HEADS * LATM_PS * sizeof(float);
-#define LATM_LAUNCH(OT_)                                                                                           \
+                            (size_t)2 * LATM_HEADS * LATM_PS * sizeof(float);
+#define LATM_LAUNCH(OT_, NW_)                                                                                         \
         do {                                                                                                       \
-            auto kern = latent_attention_mma_kernel<OT_>;                                                          \
+            auto kern = latent_attention_mma_kernel<OT_, NW_>;                                                         \
             static size_t allowed = 48 * 1024;                                                                     \
             if (smem > allowed) {                                                                                  \
                 cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
                 if (e != cudaSuccess) TQ_FAIL(-1, "latent_attention: %d bytes of shared memory refused: %s", (int)smem, cudaGetErrorString(e)); \
                 allowed = smem;                                                                                    \
             }                                                                                                      \
-            tq_launch(grid, LAT_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q_lat,                       \
+            tq_launch(grid, NW_ * 32, smem, stream)(kern, (const __nv_bfloat16*)q_lat,                             \
                 (const __nv_bfloat16*)q, q_dim, q_off, (const __nv_bfloat16*)cache, sink, positions, seq_of_token, page_table, \
                 table_stride, page_size, window, scale, (__nv_bfloat16*)out, partial, H, R, rot, n_seqs, n_pages); \
         } while (0)
-        const int OT = R / 32;
-        if (OT <= 2) { if (OT == 1) LATM_LAUNCH(1); else LATM_LAUNCH(2); }
-        else if (OT <= 4) { if (OT == 3) LATM_LAUNCH(3); else LATM_LAUNCH(4); }
-        else if (OT <= 8) { if (OT <= 6) { if (OT == 5) LATM_LAUNCH(5); else LATM_LAUNCH(6); } else { if (OT == 7) LATM_LAUNCH(7); else LATM_LAUNCH(8); } }
-        else if (OT <= 12) { if (OT <= 10) { if (OT == 9) LATM_LAUNCH(9); else LATM_LAUNCH(10); } else { if (OT == 11) LATM_LAUNCH(11); else LATM_LAUNCH(12); } }
-        else { if (OT <= 14) { if (OT == 13) LATM_LAUNCH(13); else LATM_LAUNCH(14); } else { if (OT == 15) LATM_LAUNCH(15); else LATM_LAUNCH(16); } }
+        if (R % 64 == 0) {                 // eight warps, R / 64 n-tiles each
+            switch (R / 64) {
+                case 1: LATM_LAUNCH(1, 8); break;
+                case 2: LATM_LAUNCH(2, 8); break;
+                case 3: LATM_LAUNCH(3, 8); break;
+                case 4: LATM_LAUNCH(4, 8); break;
+                case 5: LATM_LAUNCH(5, 8); break;
+                case 6: LATM_LAUNCH(6, 8); break;
+                case 7: LATM_LAUNCH(7, 8); break;
+                default: LATM_LAUNCH(8, 8); break;
+            }
+        } else {                           // four warps, an odd number of n-tiles each
+            switch (R / 32) {
+                case 1: LATM_LAUNCH(1, 4); break;
+                case 3: LATM_LAUNCH(3, 4); break;
+                case 5: LATM_LAUNCH(5, 4); break;
+                case 7: LATM_LAUNCH(7, 4); break;
+                case 9: LATM_LAUNCH(9, 4); break;
+                case 11: LATM_LAUNCH(11, 4); break;
+                case 13: LATM_LAUNCH(13, 4); break;
+                default: LATM_LAUNCH(15, 4); break;
+            }
+        }
     } else {
     dim3 grid(T_, (H + LAT_HG - 1) / LAT_HG, n_splits);
     const size_t smem = (size_t)(LAT_HG * Dk + LAT_WARPS * R) * sizeof(float);
