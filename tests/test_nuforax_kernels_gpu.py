@@ -150,16 +150,22 @@ def test_pair_embedding_remembers_the_token_before_across_steps():
         at[1] += n1
 
 
-def test_norm_on_the_sublayer_output_is_added_in_float32():
+@pytest.mark.parametrize("H", [50, 52, 1536, 4096, 4100])
+def test_norm_on_the_sublayer_output_is_added_in_float32(H):
+    """Rows of 50 and 4,100 elements take the kernel's plain form, the others the one that keeps y in registers (one,
+    two and four pieces a thread)."""
     from turboquant_cpp_b200.kernels import elementwise as K
     rng = np.random.default_rng(5)
-    x, y, w = rng.standard_normal((6, 50)) * 100, rng.standard_normal((6, 50)), 1 + 0.1 * rng.standard_normal(50)
-    xd, copy = dev(x), torch.empty((6, 50), dtype=torch.bfloat16, device=DEV)
-    want = dev(x).cpu().numpy().astype(np.float64) + P.rms(dev(y).cpu().numpy().astype(np.float64), 1e-3) * dev(w).cpu().numpy()
-    K.add_rmsnorm(xd, dev(y), dev(w), 1e-3, copy)
-    assert np.abs(xd.cpu().numpy() - want).max() < 2e-5
-    assert torch.equal(copy, xd.to(torch.bfloat16))
-    h = torch.empty((6, 50), dtype=torch.float32, device=DEV)
+    x, y, w = rng.standard_normal((6, H)) * 100, rng.standard_normal((6, H)), 1 + 0.1 * rng.standard_normal(H)
+    for with_copy in (True, False):
+        xd = dev(x)
+        copy = torch.empty((6, H), dtype=torch.bfloat16, device=DEV) if with_copy else None
+        want = dev(x).cpu().numpy().astype(np.float64) + P.rms(dev(y).cpu().numpy().astype(np.float64), 1e-3) * dev(w).cpu().numpy()
+        K.add_rmsnorm(xd, dev(y), dev(w), 1e-3, copy)
+        assert np.abs(xd.cpu().numpy() - want).max() < 2e-5
+        if with_copy:
+            assert torch.equal(copy, xd.to(torch.bfloat16))
+    h = torch.empty((6, H), dtype=torch.float32, device=DEV)
     K.map_elements(dev(y), h, K.MAP_RELU_SQUARED)
     assert np.abs(h.cpu().numpy() - P.relu_squared(dev(y).cpu().numpy().astype(np.float64))).max() < 1e-6
 

@@ -417,10 +417,70 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TY* __restrict__
     }
 }
 
+// The same for float32 y in rows of up to 4 * ADDN_THREADS * NV elements, a multiple of four: a thread keeps its
+// float4 pieces of y in registers between the sum of squares and the update, so y is read once.
+#define ADDN_THREADS 256
+template <typename TW, typename TO, int NV>
+__global__ void __launch_bounds__(ADDN_THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, const TW* __restrict__ w,
+                       TO* __restrict__ copy, int H, float eps) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    __shared__ float scratch[33];
+    const size_t r = blockIdx.x;
+    const float4* yr = reinterpret_cast<const float4*>(y + r * H);
+    float4* xr = reinterpret_cast<float4*>(x + r * H);
+    const int n4 = H / 4;
+    float4 yv[NV], xv[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        yv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            yv[k] = yr[i];
+            xv[k] = xr[i];
+        }
+        ss += yv[k].x * yv[k].x + yv[k].y * yv[k].y + yv[k].z * yv[k].z + yv[k].w * yv[k].w;
+    }
+    ss = tq_block_sum(ss, scratch);
+    const float rs = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = threadIdx.x + k * ADDN_THREADS;
+        if (i < n4) {
+            float4 v;
+            v.x = xv[k].x + yv[k].x * rs * tq_to_float(w[4 * i]);
+            v.y = xv[k].y + yv[k].y * rs * tq_to_float(w[4 * i + 1]);
+            v.z = xv[k].z + yv[k].z * rs * tq_to_float(w[4 * i + 2]);
+            v.w = xv[k].w + yv[k].w * rs * tq_to_float(w[4 * i + 3]);
+            xr[i] = v;
+            if (copy) {
+                TO* c = copy + r * H + 4 * i;
+                c[0] = tq_from_float<TO>(v.x); c[1] = tq_from_float<TO>(v.y);
+                c[2] = tq_from_float<TO>(v.z); c[3] = tq_from_float<TO>(v.w);
+            }
+        }
+    }
+}
+
 TQ_EXPORT int tq_add_rmsnorm(float* x, const void* y, int y_dtype, const void* w, int w_dtype, void* copy,
                              int copy_dtype, int R, int H, float eps, cudaStream_t stream) {
     if (R == 0) return 0;
     TQ_REQUIRE(R > 0 && H > 0, "add_rmsnorm: bad sizes R=%d H=%d", R, H);
+    if (y_dtype == TQ_F32 && H % 4 == 0 && H <= 4 * ADDN_THREADS * 4 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0) {
+        const int nv = (H / 4 + ADDN_THREADS - 1) / ADDN_THREADS;
+#define ADDN_LAUNCH(NV_)                                                                                           \
+        TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,                                                       \
+            (tq_launch(R, ADDN_THREADS, 0, stream)(add_rmsnorm_vec_kernel<TW, TO, NV_>, x, (const float*)y, (const TW*)w, \
+                                                   (TO*)copy, H, eps))))
+        if (nv <= 1) ADDN_LAUNCH(1);
+        else if (nv == 2) ADDN_LAUNCH(2);
+        else ADDN_LAUNCH(4);
+#undef ADDN_LAUNCH
+        TQ_CHECK_LAUNCH("add_rmsnorm");
+        return 0;
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     TQ_DISPATCH(y_dtype, TY, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(copy_dtype, TO,
         (tq_launch(R, threads, 0, stream)(add_rmsnorm_kernel<TY, TW, TO>, x, (const TY*)y, (const TW*)w, (TO*)copy, H,
