@@ -306,6 +306,7 @@ TQ_EXPORT int tq_ssm_scan(const float* xbc, int C, const float* proj, int P, int
 // out[t, g-th part] = rms(y[t, part] * silu(z[t, part])) * w[part]: the gate first, then the norm of each of the
 // `norm_groups` equal parts by its own root mean square.  z is the first `inner` elements of the projection's row.
 // ---------------------------------------------------------------------------------------
+#define GGN_KEEP 8
 template <typename TW, typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int P, int z_off,
                                         const TW* __restrict__ w, TO* __restrict__ out, int inner, int gs, float eps) {
@@ -316,14 +317,32 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
     const int base = blockIdx.y * gs;
     const float* yr = y + t * inner + base;
     const float* zr = proj + t * P + z_off + base;
+    // a thread's gated values stay in registers between the sum of squares and the output (up to GGN_KEEP of them;
+    // longer parts compute the rest again)
+    float keep[GGN_KEEP];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < GGN_KEEP; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        keep[k] = 0.f;
+        if (i < gs) {
+            const float z = zr[i];
+            keep[k] = yr[i] * (z / (1.0f + expf(-z)));
+        }
+        ss += keep[k] * keep[k];
+    }
+    for (int i = threadIdx.x + GGN_KEEP * blockDim.x; i < gs; i += blockDim.x) {
         const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
         ss += v * v;
     }
     ss = tq_block_sum(ss, scratch);
     const float rs = 1.0f / sqrtf(ss / (float)gs + eps);
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < GGN_KEEP; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < gs) out[t * inner + base + i] = tq_from_float<TO>(keep[k] * rs * tq_to_float(w[base + i]));
+    }
+    for (int i = threadIdx.x + GGN_KEEP * blockDim.x; i < gs; i += blockDim.x) {
         const float z = zr[i], v = yr[i] * (z / (1.0f + expf(-z)));
         out[t * inner + base + i] = tq_from_float<TO>(v * rs * tq_to_float(w[base + i]));
     }
