@@ -143,6 +143,12 @@ class LatentAttentionMixer(Mixer):
         H, R, Dk = self.heads, self.kv_rank, self.kv_rank + self.rot_dim
         act, dev = qa.dtype, qa.device
         block = max(16, self.PROMPT_ROWS // H)
+        # one buffer for the gathered rows and one for the weights, sized for the widest block of the step
+        longest = max(ctx.host_q_lens)
+        most = min(block, longest) + (self.window - 1 if self.window else ctx.max_kv_len)
+        most = -(-min(most, ctx.max_kv_len) // 64) * 64
+        rows_all = torch.empty((most, Dk), dtype=act, device=dev)
+        weights_all = torch.empty(min(block, longest) * H * most, dtype=act, device=dev)
         t0 = 0
         for i, (n, start) in enumerate(zip(ctx.host_q_lens, ctx.host_seq_start)):
             for a in range(0, n, block):
@@ -153,12 +159,12 @@ class LatentAttentionMixer(Mixer):
                 # padded with zero rows, which the softmax gives weight 0 (they lie behind the block's last position)
                 n_keys = k1 - k0
                 n_pad = -(-n_keys // 64) * 64
-                rows = torch.empty((n_pad, Dk), dtype=act, device=dev)
+                rows = rows_all[:n_pad]
                 KL.latent_gather(cache.kv, cache.page_table[i], cache.page_size, k0, n_keys, rows[:n_keys])
                 if n_pad > n_keys:
                     rows[n_keys:].zero_()
                 scores = product(qa[t0 + a:t0 + b].view(-1, Dk), rows.t(), out_dtype=torch.float32)
-                weights = torch.empty(scores.shape, dtype=act, device=dev)
+                weights = weights_all[:scores.shape[0] * n_pad].view(scores.shape[0], n_pad)
                 KL.latent_softmax(scores, self.sink, self.scale, self.window, pos0, k0, H, weights)
                 product(weights, rows[:, :R], out=sums[t0 + a:t0 + b].view(-1, R))
             t0 += n
