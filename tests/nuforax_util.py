@@ -38,7 +38,7 @@ def config(layers, vocab=97, width=48, eps=1e-5, scale=4.0, bigram=(53, 5, 3)):
 
 YARN = {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}
 
-# Three configurations that differ in every size, in the order and kinds of layers, and in the options.
+# Four configurations that differ in every size, in the order and kinds of layers, and in the options.
 CONFIGS = {
     # attention first, a reader of its rows with a narrower window, a state-space layer with a feed-forward
     "a": config([layer("latent_attention", latent(scaling=YARN), ff=80),
@@ -59,6 +59,14 @@ CONFIGS = {
                  layer("latent_attention", latent(heads=1, dim=32, rot_dim=32, vdim=32, kv_rank=288, window=65, scale=0.2,
                                                   base=500000.0, scaling={"factor": 8.0, "original": 32, "fast": 16.0, "slow": 2.0}, kv_from=0))],
                 vocab=128, width=64, bigram=(31, 1, 1)),
+    # a latent of 128 elements (in bfloat16 the tensor-core form with eight warps a block), six heads, a reader with
+    # a wider window behind a state-space layer with as many groups as heads
+    "d": config([layer("latent_attention", latent(heads=6, dim=24, rot_dim=32, vdim=20, kv_rank=128, window=50, scale=0.25,
+                                                  scaling=YARN), ff=100),
+                 layer("mamba2", mamba(heads=4, vdim=16, state=32, groups=4, conv=4, norm_groups=1), ff=48),
+                 layer("latent_attention", latent(heads=6, dim=24, rot_dim=32, vdim=20, kv_rank=128, window=90, scale=0.25,
+                                                  scaling=YARN, kv_from=0))],
+                vocab=111, width=72, bigram=(29, 3, 11)),
 }
 
 

@@ -44,7 +44,7 @@ def engine_for(folder, dtype, max_tokens=1024, **kw):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_whole_prompts_decoding_and_batches_agree_with_plain(folders, name, dtype):
     cfg, folder = CONFIGS[name], folders[name]
     reqs = {"r0": tokens_for(cfg, 150, 1), "r1": tokens_for(cfg, 1, 2), "r2": tokens_for(cfg, 77, 3), "r3": tokens_for(cfg, 200, 4)}
