@@ -226,3 +226,34 @@ def test_gate_comes_before_the_group_norm(T, inner, groups):
     g = f32(y) * P.silu(f32(proj)[:, :inner])
     want = P.rms(g.reshape(T, groups, -1), 1e-5).reshape(T, inner) * f32(w)
     assert np.abs(out.cpu().numpy() - want).max() < 1e-5
+
+
+@pytest.mark.parametrize("H,R,rot,lead", [(16, 512, 64, 128), (6, 128, 32, 24), (20, 64, 16, 8), (5, 160, 32, 16), (3, 32, 0, 8),
+                                           (7, 64, 48, 8), (9, 448, 32, 64)])
+def test_tensor_core_form_agrees_with_the_float32_token_form(H, R, rot, lead):
+    """The same bfloat16-rounded queries and rows through the bfloat16 kernel (tensor-core form at these sizes: four or
+    eight warps, odd and even numbers of 16-element steps, one to eight output tiles a warp) and through the float32
+    token form: they may differ by the rounding of the weights and of the output (2^-8 of a row's largest element),
+    which a dropped step of a row or a key's wrong place would exceed many times."""
+    from turboquant_cpp_b200.kernels import latent_attention as KL
+    assert KL.tensor_core_form(torch.bfloat16, R, rot)
+    gen = torch.Generator(device="cpu").manual_seed(R + rot)
+    T, window, ctx, ps = 6, 700, 1500, 64
+    Dk, pages_per = R + rot, 1500 // 64 + 1
+    r32 = lambda *shape, s: (torch.randn(shape, generator=gen) * s).to(torch.bfloat16).float().to(DEV)
+    cache32 = r32(T * pages_per, 1, 1, ps, Dk, s=0.5)
+    table = torch.arange(T * pages_per, dtype=torch.int32, device=DEV).view(T, pages_per)
+    q_lat32, q32 = r32(T, H, R, s=0.15), r32(T, H * (lead + rot), s=0.15)
+    sink = torch.randn(H, generator=gen).to(DEV)
+    pos, seq = i32([ctx - 1, 0, 5, window, window - 1, 1234]), i32(list(range(T)))
+    for n_splits in (1, 5):
+        outs = {}
+        for dt in (torch.float32, torch.bfloat16):
+            out = torch.empty((T, H, R), dtype=dt, device=DEV)
+            partial = torch.empty(T * H * n_splits * (R + 2), dtype=torch.float32, device=DEV)
+            KL.latent_attention(q_lat32.to(dt), q32.to(dt), lead, cache32.to(dt), sink, pos, seq, table, ps, window, 0.11, out,
+                                H, R, rot, n_splits, partial)
+            outs[dt] = out.float()
+        ref, got = outs[torch.float32], outs[torch.bfloat16]
+        err = ((got - ref).abs() / ref.abs().amax(dim=-1, keepdim=True)).max().item()
+        assert err < 6e-3, f"{n_splits} ranges: {err:.2e}"
