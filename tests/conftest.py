@@ -17,6 +17,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
+@pytest.fixture(autouse=True)
+def seeded_by_name(request):
+    """Every test starts from torch generators (CPU and CUDA) seeded by its own name, so what a test draws does not
+    depend on which tests ran before it."""
+    import zlib
+
+    import torch
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()))
+    yield
+
+
 # Two tiny configurations that differ in every size and option, and a third with odd sizes
 # (a head size that is not hidden/heads, one KV head, no shared expert, a dense layer by sparse step).
 TINY_A = {
