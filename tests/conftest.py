@@ -24,7 +24,8 @@ def seeded_by_name(request):
     import zlib
 
     import torch
-    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()))
+    # the file's own name and the test's, not a path: the same numbers from whatever folder pytest is started
+    torch.manual_seed(zlib.crc32(f"{os.path.basename(str(request.node.fspath))}::{request.node.name}".encode()))
     yield
 
 
