@@ -69,12 +69,16 @@ class Sequence_:
 
 
 class CacheBook:
-    """Pages and slots of all groups.  ``windows[g]`` is the window of group g (0: keeps all)."""
+    """Pages and slots of all groups.  ``windows[g]`` is the window of group g (0: keeps all);
+    ``keep_first[g]`` positions at a sequence's start stay in a windowed group for good."""
 
-    def __init__(self, n_pages: Sequence[int], windows: Sequence[int], page_size: int, max_slots: int):
+    def __init__(self, n_pages: Sequence[int], windows: Sequence[int], page_size: int, max_slots: int,
+                 keep_first: Optional[Sequence[int]] = None):
         assert len(n_pages) == len(windows)
         self.page_size = int(page_size)
         self.windows = [int(w) for w in windows]
+        self.keep_first = [int(k) for k in keep_first] if keep_first is not None else [0] * len(self.windows)
+        assert len(self.keep_first) == len(self.windows)
         self.pools = [IndexPool(n, f"page of group {g}") for g, n in enumerate(n_pages)]
         self.slots = IndexPool(max_slots, "sequence slot")
         self._next_id = 0
@@ -113,14 +117,16 @@ class CacheBook:
 
     def commit(self, seq: Sequence_, n_new: int) -> None:
         """The step wrote n_new tokens.  A windowed group gives back the pages no later query can see:
-        a query at position p >= length reads positions >= p + 1 - window."""
+        a query at position p >= length reads positions >= p + 1 - window, and the group's first keep_first
+        positions (their pages are never given back)."""
         self._check_open(seq)
         seq.length += n_new
         for g, w in enumerate(self.windows):
             if w <= 0:
                 continue
             first_visible = max(0, seq.length + 1 - w)
-            for i in range(min(first_visible // self.page_size, len(seq.pages[g]))):
+            kept = -(-self.keep_first[g] // self.page_size)
+            for i in range(kept, min(first_visible // self.page_size, len(seq.pages[g]))):
                 if seq.pages[g][i] is not None:
                     self.pools[g].give_back(seq.pages[g][i])
                     seq.pages[g][i] = None

@@ -60,7 +60,8 @@ class PagedCache:
             if src is not None:
                 self.entry_group[i] = self.entry_group[src]
         counts = [(pages_per_group or {}).get(g, n_pages) for g in self.groups]
-        self.book = CacheBook(counts, [g.window for g in self.groups], self.page_size, self.max_slots)
+        self.book = CacheBook(counts, [g.window for g in self.groups], self.page_size, self.max_slots,
+                              keep_first=[g.keep_first for g in self.groups])
         self.kv: List[Optional[torch.Tensor]] = []
         for i, need in enumerate(kv_needs):
             if need is None or cache_of[i] is not None:

@@ -257,10 +257,10 @@ TQ_EXPORT int tq_add_bias(void* x, int x_dtype, const void* bias, int bias_dtype
 }
 
 // ---------------------------------------------------------------------------------------
-// h[t, i] = silu(gu[t, i]) * gu[t, I + i]   (gate rows first, then up rows)
+// h[t, i] = glu(gu[t, i], gu[t, I + i])   (gate rows first, then up rows; glu: common.cuh, silu(gate) * up by default)
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>
-__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, int I) {
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, int I, TqGlu act) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     const int t = blockIdx.x;
@@ -268,15 +268,28 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ h, i
     TO* o = h + (size_t)t * I;
     for (int i = threadIdx.x; i < I; i += blockDim.x) {
         const float a = tq_to_float(g[i]), b = tq_to_float(g[I + i]);
-        o[i] = tq_from_float<TO>(a / (1.0f + expf(-a)) * b);
+        o[i] = tq_from_float<TO>(tq_glu(a, b, act));
     }
+}
+
+// limit <= 0: no caps.  (limit, slope, offset) = (0, 1, 0): silu(gate) * up.
+TQ_EXPORT int tq_glu_mul(const void* gu, int in_dtype, void* h, int out_dtype, int T_, int I, float limit, float slope,
+                         float offset, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(T_ > 0 && I > 0, "glu_mul: bad sizes T=%d I=%d", T_, I);
+    const TqGlu act = tq_glu_params(limit, slope, offset);
+    TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
+        (tq_launch(T_, 256, 0, stream)(silu_mul_kernel<TI, TO>, (const TI*)gu, (TO*)h, I, act))));
+    TQ_CHECK_LAUNCH("glu_mul");
+    return 0;
 }
 
 TQ_EXPORT int tq_silu_mul(const void* gu, int in_dtype, void* h, int out_dtype, int T_, int I, cudaStream_t stream) {
     if (T_ == 0) return 0;
     TQ_REQUIRE(T_ > 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T_, I);
+    const TqGlu act = tq_glu_params(0.f, 1.f, 0.f);
     TQ_DISPATCH(in_dtype, TI, TQ_DISPATCH(out_dtype, TO,
-        (tq_launch(T_, 256, 0, stream)(silu_mul_kernel<TI, TO>, (const TI*)gu, (TO*)h, I))));
+        (tq_launch(T_, 256, 0, stream)(silu_mul_kernel<TI, TO>, (const TI*)gu, (TO*)h, I, act))));
     TQ_CHECK_LAUNCH("silu_mul");
     return 0;
 }

@@ -188,11 +188,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 // silu(gate) * up.  A bfloat16 result keeps 8 bits, so the fast exponential and division (a few units in
 // the last place of fp32) do; an fp32 result gets the exact ones.
-template <typename TO> __device__ __forceinline__ float silu_mul(float gate, float up) {
-    return gate / (1.0f + expf(-gate)) * up;
+// The general gated form (common.cuh: caps, slope, offset) with the same choice of exponential and division.
+template <typename TO> __device__ __forceinline__ float silu_mul(float gate, float up, TqGlu p) {
+    return tq_glu(gate, up, p);
 }
-template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float gate, float up) {
-    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float gate, float up, TqGlu p) {
+    const float g = fminf(gate, p.limit), u = fminf(fmaxf(up, -p.limit), p.limit);
+    return __fdividef(g, 1.0f + __expf(-p.slope * g)) * (u + p.offset);
 }
 
 template <int BN, bool PAIR>
@@ -276,6 +278,7 @@ struct Second {
     CUtensorMap map_w, map_x, map_x_tail;
     void* out;
     int R, N, K;
+    TqGlu act;          // the second product's gated activation (SwiGLU launches)
     int first;          // 0: the second product's tiles are spread evenly among the first's; 1: they all come first
 };
 
@@ -304,7 +307,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const __grid_constant__ CUtensorMap map_x_tail, TO* __restrict__ out,
                const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                const int* __restrict__ tile_count, const int* __restrict__ n_tiles, int R, int N, int K,
-               int stream_weights, int* __restrict__ status, int k_splits, const __grid_constant__ SECOND second) {
+               int stream_weights, int* __restrict__ status, int k_splits, TqGlu act, const __grid_constant__ SECOND second) {
     // Bit 1 of stream_weights: the weights, the tile list and the sizes were final before the kernel ahead of this
     // one in the stream started (a down projection behind its gate/up product; a product with one group), so the
     // thread that streams the weights does not wait for that kernel: its loads are in flight while the kernel ahead
@@ -563,7 +566,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int n = (PAIR ? 2 * t.mx + (int)rank : t.mx) * COLS + r;           // output column
             TO* out_u = KSPLIT ? out + (size_t)(u / total) * R * N : out;            // this share's slice (kb0, kb1 unused here)
             int Nn = N;                                                              // width of this product's output
-            if constexpr (DUAL) if (is2) { out_u = (TO*)second.out; Nn = N2; }
+            TqGlu act_u = act;
+            if constexpr (DUAL) if (is2) { out_u = (TO*)second.out; Nn = N2; act_u = second.act; }
             (void)kb0; (void)kb1;
             ok = __all_sync(0xffffffffu, mbar_wait(acc_full(b), (uint32_t)(it >> 1) & 1u, &s_abort));   // warp-uniform
             if (!ok) break;
@@ -587,7 +591,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const float gate = __uint_as_float(high ? got : g[j]);
                         const float up = __uint_as_float(high ? g[8 + j] : got);
                         const int c = c0 + j + (high ? 8 : 0);
-                        if (n < Nn && c < t.count) out_u[(size_t)(t.row0 + c) * Nn + n] = tq_from_float<TO>(silu_mul<TO>(gate, up));
+                        if (n < Nn && c < t.count) out_u[(size_t)(t.row0 + c) * Nn + n] = tq_from_float<TO>(silu_mul<TO>(gate, up, act_u));
                     }
                 } else if (n < Nn) {
 #pragma unroll
@@ -667,7 +671,8 @@ int make_map_w(CUtensorMap* map, const void* ptr, uint64_t k_blocks, uint64_t ti
 template <int BN, bool SWIGLU, typename TO, bool PAIR, bool KSPLIT = false, typename SECOND = NoSecond>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt, void* out, const int* te, const int* tr,
            const int* tc, const int* nt, int grid_y, int R, int N, int K, int G, int* status, int sm_share_pct,
-           int k_splits, cudaStream_t stream, const SECOND& second = SECOND(), long long tiles2 = 0, int early_weights = 0) {
+           int k_splits, cudaStream_t stream, const SECOND& second = SECOND(), long long tiles2 = 0, int early_weights = 0,
+           TqGlu act = TqGlu{INFINITY, 1.0f, 0.0f}) {
     using T = Tile<BN, PAIR>;
     auto kern = gemm_tc_kernel<BN, SWIGLU, TO, PAIR, KSPLIT, SECOND>;
     static bool configured = false;
@@ -709,7 +714,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
     const int grid = (int)(want < room ? want : room);
     tq_launch(grid, T::THREADS, T::SMEM_BYTES, stream, PAIR ? 2 : 1)(kern, mw, mx, mxt, (TO*)out, te, tr, tc, nt, R, N, K,
         /* stream_weights: on average at most one token tile per group */ ((te != nullptr && (long long)R <= (long long)G * BN) ? 1 : 0) | (early_weights ? 2 : 0), status,
-        k_splits, second);
+        k_splits, act, second);
     TQ_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -731,8 +736,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mxt,
 TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype, const int* tile_expert,
                          const int* tile_row0, const int* tile_count, const int* n_tiles, int max_tiles, int bn,
                          int R, int N, int K, int G, int swiglu, int pair, int* status, int sm_share_pct,
-                         int k_splits, int early_weights, cudaStream_t stream) {
+                         int k_splits, int early_weights, float glu_limit, float glu_slope, float glu_offset,
+                         cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
+    const TqGlu act = tq_glu_params(glu_limit, glu_slope, glu_offset);       // (0, 1, 0): silu(gate) * up
     TQ_REQUIRE(k_splits >= 1, "gemm_tc: %d shares of K", k_splits);
     if (k_splits > 1) {
         TQ_REQUIRE(!swiglu && out_dtype == TQ_F32, "gemm_tc: K is shared out only for plain products with float32 partial sums");
@@ -755,7 +762,7 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
     if (rc) return rc;
     rc = make_map_x(&mxt, X, (uint64_t)K, (uint64_t)R, 16u);
     if (rc) return rc;
-#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, sm_share_pct, k_splits, stream, NoSecond(), 0, early_weights
+#define TC_ARGS mw, mx, mxt, out, tile_expert, tile_row0, tile_count, n_tiles, grid_y, R, N, K, G, status, sm_share_pct, k_splits, stream, NoSecond(), 0, early_weights, act
 #define TC_CASE(BN_, PAIR_)                                                                          \
     if (bn == BN_ && (pair != 0) == PAIR_) {                                                         \
         if (swiglu) {                                                                                \
@@ -786,7 +793,9 @@ TQ_EXPORT int tq_gemm_tc(const void* X, const void* W, void* out, int out_dtype,
 TQ_EXPORT int tq_gemm_tc_dual(const void* X, const void* W, void* out, const int* tile_expert, const int* tile_row0,
                               const int* tile_count, const int* n_tiles, int max_tiles, int R, int N, int K, int G,
                               const void* X2, const void* W2, void* out2, int R2, int N2, int K2, int out_dtype,
-                              int bn, int swiglu, int* status, int second_first, cudaStream_t stream) {
+                              int bn, int swiglu, int* status, int second_first, float glu_limit, float glu_slope,
+                              float glu_offset, float glu_limit2, cudaStream_t stream) {
+    const TqGlu act = tq_glu_params(glu_limit, glu_slope, glu_offset);       // the second product: its own caps
     TQ_REQUIRE(tile_expert && tile_row0 && tile_count && n_tiles, "gemm_tc_dual: the first product needs a layout");
     TQ_REQUIRE(R > 0 && N > 0 && K > 0 && G > 0 && R2 > 0 && N2 > 0 && K2 > 0, "gemm_tc_dual: bad sizes R=%d N=%d K=%d G=%d, R2=%d N2=%d K2=%d", R, N, K, G, R2, N2, K2);
     TQ_REQUIRE(K % 8 == 0 && K2 % 8 == 0, "gemm_tc_dual: K=%d and K2=%d must be multiples of 8 (16-byte rows for TMA)", K, K2);
@@ -796,7 +805,7 @@ TQ_EXPORT int tq_gemm_tc_dual(const void* X, const void* W, void* out, const int
     TQ_REQUIRE((swiglu && out_dtype == TQ_BF16) || (!swiglu && out_dtype == TQ_F32),
                "gemm_tc_dual: SwiGLU products write bfloat16 and plain products float32 (got swiglu=%d, type %d)", swiglu, out_dtype);
     TQ_REQUIRE(status != nullptr, "gemm_tc_dual: a status word is required");
-    if (max_tiles == 0) return tq_gemm_tc(X2, W2, out2, out_dtype, nullptr, nullptr, nullptr, nullptr, 0, bn, R2, N2, K2, 1, swiglu, 1, status, 0, 1, 0, stream);
+    if (max_tiles == 0) return tq_gemm_tc(X2, W2, out2, out_dtype, nullptr, nullptr, nullptr, nullptr, 0, bn, R2, N2, K2, 1, swiglu, 1, status, 0, 1, 0, glu_limit2, glu_slope, glu_offset, stream);
     const int cols = swiglu ? BM / 2 : BM;
     const int n_m1 = (N + cols - 1) / cols, n_m1_2 = (N2 + cols - 1) / cols;
     CUtensorMap mw, mx, mxt;
@@ -809,13 +818,14 @@ TQ_EXPORT int tq_gemm_tc_dual(const void* X, const void* W, void* out, const int
     if ((rc = make_map_x(&sec.map_x, X2, (uint64_t)K2, (uint64_t)R2, 64u))) return rc;
     if ((rc = make_map_x(&sec.map_x_tail, X2, (uint64_t)K2, (uint64_t)R2, 16u))) return rc;
     sec.out = out2; sec.R = R2; sec.N = N2; sec.K = K2; sec.first = second_first ? 1 : 0;
+    sec.act = tq_glu_params(glu_limit2, glu_slope, glu_offset);
     const long long tiles2 = (long long)((n_m1_2 + 1) / 2) * ((R2 + bn - 1) / bn);
 #define TC_DUAL(BN_)                                                                                                       \
     if (bn == BN_) {                                                                                                       \
         if (swiglu) return launch<BN_, true, __nv_bfloat16, true, false, Second>(mw, mx, mxt, out, tile_expert, tile_row0, \
-            tile_count, n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2);                                \
+            tile_count, n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2, 0, act);                              \
         return launch<BN_, false, float, true, false, Second>(mw, mx, mxt, out, tile_expert, tile_row0, tile_count,        \
-            n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2);                                            \
+            n_tiles, max_tiles, R, N, K, G, status, 0, 1, stream, sec, tiles2, 0, act);                                          \
     }
     TC_DUAL(128) TC_DUAL(256)
 #undef TC_DUAL

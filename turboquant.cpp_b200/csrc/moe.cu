@@ -273,6 +273,137 @@ TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* share
     return 0;
 }
 
+// Selection with a correction of the choice and groups of experts, one warp per token.  s = softmax(logits) over all
+// E experts; the choice looks at c = s + correction (correction may be null: c = s); with n_groups > 1 the experts form
+// n_groups equal groups of neighbours, a group's value is its largest c, and only experts of the keep_groups groups
+// with the largest values can be chosen (the others count as minus infinity); the k largest c are chosen (ties to
+// the lowest index); the weights are the chosen experts' s, divided by (their sum + floor) if renorm.
+// choice: T * E floats of scratch; group_best: T * n_groups floats of scratch (n_groups > 1).
+__global__ void router_select_corrected_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                               float* __restrict__ choice, float* __restrict__ group_best,
+                                               int* __restrict__ ids, float* __restrict__ wts,
+                                               float* __restrict__ shared_scale, int T_, int E, int k, int renorm,
+                                               float floor_, int n_groups, int keep_groups) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T_) return;
+    const float* row = logits + (size_t)t * (E + 1);
+    float* c = choice + (size_t)t * E;
+    if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+    mx = tq_warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(row[e] - mx);
+    sum = tq_warp_sum(sum);
+    for (int e = lane; e < E; e += 32) c[e] = expf(row[e] - mx) / sum + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    if (n_groups > 1) {
+        const int per = E / n_groups;
+        float* gb = group_best + (size_t)t * n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+            gb[g] = b;
+        }
+        __syncwarp();
+        for (int j = 0; j < keep_groups; ++j) {          // the kept groups are marked with +inf
+            float best = -INFINITY;
+            int best_g = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gb[g];
+                if (v != INFINITY && (v > best || (v == best && g < best_g) || best_g == 0x7fffffff) && v == v) { best = v; best_g = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                if (og != 0x7fffffff && (best_g == 0x7fffffff || ov > best || (ov == best && og < best_g))) { best = ov; best_g = og; }
+            }
+            if (best_g != 0x7fffffff && lane == 0) gb[best_g] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (gb[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    float picked_sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }   // NaN and minus infinity never win
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        const bool found = best_e != 0x7fffffff && best != -INFINITY;
+        if (!found) best_e = j;                  // nothing left that may be chosen: keep indices valid, weight 0
+        const float p = found ? expf(row[best_e] - mx) / sum : 0.f;
+        picked_sum += p;                         // identical in every lane
+        if (lane == 0) {
+            ids[(size_t)t * k + j] = best_e;
+            wts[(size_t)t * k + j] = p;
+            if (found) c[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (renorm) {
+        __syncwarp();
+        for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / (picked_sum + floor_);
+    }
+}
+
+TQ_EXPORT int tq_router_select_corrected(const float* logits, const float* correction, float* choice, float* group_best,
+                                         int* ids, float* wts, float* shared_scale, int T_, int E, int k, int renorm,
+                                         float floor_, int n_groups, int keep_groups, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
+    TQ_REQUIRE(k >= 1 && k <= E, "router: top-k %d must be in 1..%d", k, E);
+    TQ_REQUIRE(choice != nullptr, "router: scratch for the choice values is required");
+    TQ_REQUIRE(n_groups >= 1 && E % n_groups == 0, "router: %d experts do not form %d equal groups", E, n_groups);
+    TQ_REQUIRE(n_groups == 1 || (keep_groups >= 1 && keep_groups <= n_groups && group_best != nullptr),
+               "router: %d of %d groups kept", keep_groups, n_groups);
+    TQ_REQUIRE(n_groups == 1 || keep_groups * (E / n_groups) >= k, "router: %d groups of %d experts cannot give %d choices",
+               keep_groups, E / n_groups, k);
+    tq_launch((T_ + 3) / 4, 128, 0, stream)(router_select_corrected_kernel, logits, correction, choice, group_best, ids, wts,
+                                            shared_scale, T_, E, k, renorm, floor_, n_groups, keep_groups);
+    TQ_CHECK_LAUNCH("router_select_corrected");
+    return 0;
+}
+
+// The logits alone (what tq_router_topk computes before it chooses): logits [T, E + 1], column E the shared gate's.
+TQ_EXPORT int tq_router_logits(const void* x, int act_dtype, const void* wr, const void* wsg, int w_dtype,
+                               float* logits, int T_, int H, int E, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(E >= 1 && E <= ROUTER_MAX_EXPERTS, "router: %d experts exceed %d", E, ROUTER_MAX_EXPERTS);
+    const bool staged = H <= ROUTER_MAX_STAGED_H;
+    const size_t smem = staged ? (size_t)H * sizeof(float) : 0;
+    const int wbytes = w_dtype == TQ_F32 ? 4 : 2;
+    const int vec_ok = ((size_t)H * wbytes) % 16 == 0 && ((uintptr_t)wr % 16) == 0 && (!wsg || ((uintptr_t)wsg % 16) == 0);
+    const int rows = E + (wsg ? 1 : 0);
+    int chunks = T_ >= 256 ? 1 : (512 + T_ - 1) / T_;
+    if (chunks > (rows + 3) / 4) chunks = (rows + 3) / 4;
+    if (chunks < 1) chunks = 1;
+    const int rows_per_cta = (rows + chunks - 1) / chunks;
+    chunks = (rows + rows_per_cta - 1) / rows_per_cta;
+    const int threads = rows_per_cta >= 32 ? 1024 : (rows_per_cta >= 16 ? 512 : (rows_per_cta >= 8 ? 256 : 128));
+    dim3 grid(T_, chunks);
+#define ROUTER_LAUNCH(ST)                                                                              \
+    TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,                                                \
+        (tq_launch(grid, threads, smem, stream)(router_logits_kernel<TA, TW, ST>,                             \
+            (const TA*)x, (const TW*)wr, (const TW*)wsg, logits, H, E, rows_per_cta, vec_ok))))
+    if (staged) { ROUTER_LAUNCH(true); } else { ROUTER_LAUNCH(false); }
+#undef ROUTER_LAUNCH
+    TQ_CHECK_LAUNCH("router_logits");
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // Expert-sorted layout.  Pair p = t*k + j chose expert ids[p].  Rows of the sorted layout:
 // expert 0's pairs in pair order, then expert 1's, …  Outputs:
@@ -972,7 +1103,7 @@ __global__ void __launch_bounds__(256)
 grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ C,
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ tile_count, const int* __restrict__ n_tiles,
-                    int R, int N, int K) {
+                    int R, int N, int K, TqGlu act) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     __shared__ float As[GG_BK][GG_BM + 4];
@@ -1047,7 +1178,7 @@ grouped_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
             float v;
             if (SWIGLU) {
                 const float g = acc[0][i][j], u = acc[SWIGLU ? 1 : 0][i][j];
-                v = g / (1.0f + expf(-g)) * u;
+                v = tq_glu(g, u, act);
             } else {
                 v = acc[0][i][j];
             }
@@ -1087,7 +1218,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32)
 grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __restrict__ C,
                     const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                     const int* __restrict__ tile_count, const int* __restrict__ n_tiles,
-                    int R, int N, int K, int tile_rows, int vec) {
+                    int R, int N, int K, int tile_rows, int vec, TqGlu act) {
     tq_grid_wait();                    // everything below may read what the previous kernel wrote
     tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
     extern __shared__ __align__(16) float s_rows[];          // [GV_ROWS][GV_KC]
@@ -1179,7 +1310,7 @@ grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
                         float v = tq_warp_sum(acc[c][0][r]);
                         if (SWIGLU) {
                             const float u = tq_warp_sum(acc[c][S - 1][r]);
-                            v = v / (1.0f + expf(-v)) * u;
+                            v = tq_glu(v, u, act);
                         }
                         if (lane == 0) C[(size_t)(row0 + rb + r) * N + n] = tq_from_float<TO>(v);
                     }
@@ -1193,7 +1324,7 @@ grouped_gemv_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TO* __re
 // tq_grouped_gemm.
 template <typename TA, typename TW, typename TO, bool SWIGLU>
 int launch_grouped_gemv(const void* A, const void* W, void* C, const int* te, const int* tr, const int* tc, const int* nt,
-                        int by, int R, int N, int K, int tile_rows, cudaStream_t stream) {
+                        int by, int R, int N, int K, int tile_rows, TqGlu act, cudaStream_t stream) {
     auto kern = grouped_gemv_kernel<TA, TW, TO, SWIGLU>;
     const int smem = GV_ROWS * GV_KC * (int)sizeof(float);
     static bool configured = false;
@@ -1206,15 +1337,16 @@ int launch_grouped_gemv(const void* A, const void* W, void* C, const int* te, co
     dim3 grid((N + cols - 1) / cols, by);
     // 16-byte (8-byte) loads of four weights: rows of K values that start on such a boundary
     const int vec = K % 4 == 0 && ((uintptr_t)W % (4 * sizeof(TW))) == 0;
-    tq_launch(grid, GV_WARPS * 32, smem, stream)(kern, (const TA*)A, (const TW*)W, (TO*)C, te, tr, tc, nt, R, N, K, tile_rows, vec);
+    tq_launch(grid, GV_WARPS * 32, smem, stream)(kern, (const TA*)A, (const TW*)W, (TO*)C, te, tr, tc, nt, R, N, K, tile_rows, vec, act);
     return 0;
 }
 
 TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
                               const int* tile_expert, const int* tile_row0, const int* tile_count,
                               const int* n_tiles, int max_tiles, int R, int N, int K, int swiglu, int few_rows,
-                              cudaStream_t stream) {
+                              float glu_limit, float glu_slope, float glu_offset, cudaStream_t stream) {
     if (R == 0 || (tile_expert && max_tiles == 0)) return 0;
+    const TqGlu act = tq_glu_params(glu_limit, glu_slope, glu_offset);      // (0, 1, 0): silu(gate) * up
     TQ_REQUIRE(R > 0 && N > 0 && K > 0, "grouped_gemm: bad sizes R=%d N=%d K=%d", R, N, K);
     const int by = tile_expert ? max_tiles : (R + GG_BM - 1) / GG_BM;
     TQ_REQUIRE(by <= 65535, "grouped_gemm: %d row tiles exceed the grid limit", by);
@@ -1225,8 +1357,8 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
     if (few_rows && gv_types) {
         int rc = 0;
 #define GV_LAUNCH(TA, TW, TO)                                                                                     \
-        rc = swiglu ? launch_grouped_gemv<TA, TW, TO, true>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream) \
-                    : launch_grouped_gemv<TA, TW, TO, false>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, stream)
+        rc = swiglu ? launch_grouped_gemv<TA, TW, TO, true>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, act, stream) \
+                    : launch_grouped_gemv<TA, TW, TO, false>(A, W, C, tile_expert, tile_row0, tile_count, n_tiles, by, R, N, K, GG_BM, act, stream)
         if (a_dtype == TQ_F32) GV_LAUNCH(float, float, float);
         else if (c_dtype == TQ_F32) GV_LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
         else GV_LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
@@ -1239,7 +1371,7 @@ TQ_EXPORT int tq_grouped_gemm(const void* A, int a_dtype, const void* W, int w_d
 #define GG_LAUNCH(SW)                                                                                   \
     TQ_DISPATCH(a_dtype, TA, TQ_DISPATCH(w_dtype, TW, TQ_DISPATCH(c_dtype, TO,                          \
         (tq_launch(grid, 256, 0, stream)(grouped_gemm_kernel<TA, TW, TO, SW>,                                  \
-            (const TA*)A, (const TW*)W, (TO*)C, tile_expert, tile_row0, tile_count, n_tiles, R, N, K)))))
+            (const TA*)A, (const TW*)W, (TO*)C, tile_expert, tile_row0, tile_count, n_tiles, R, N, K, act)))))
     if (swiglu) { GG_LAUNCH(true); } else { GG_LAUNCH(false); }
 #undef GG_LAUNCH
     TQ_CHECK_LAUNCH("grouped_gemm");

@@ -1,0 +1,83 @@
+"""Launchers of csrc/bias_attention.cu: attention with a distance bias, a window that keeps a sequence's first
+positions and a sink in the softmax, over cache rows that hold a key and a value of different sizes."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_kernel
+from ._call import KernelError, check, code, ptr, stream, want_f32, want_int32
+
+_LIB = "bias_attention"
+MAX_DIM = 256        # csrc/bias_attention.cu BA_MAX_DIM: the most elements of a key or of a value
+
+
+def kv_write(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Tensor], v_keep: Optional[torch.Tensor],
+             v_other: Optional[torch.Tensor], mix: float, positions: torch.Tensor, seq_of_token: torch.Tensor,
+             page_table: torch.Tensor, page_size: int, heads: int, kv_heads: int, dk: int, dv: int) -> None:
+    """qkv float32 [T, heads * dk + kv_heads * (dk + dv)], the fused projection [q | k | v]: queries go to q_out
+    [T, heads, dk] (activation dtype), keys and values to the token's place in cache [pages, 1, kv_heads, page_size,
+    dk + dv].  v_other float32 [T, kv_heads * dv]: the values become (1 - mix) v + mix v_other first; v_keep (same
+    shape) receives the values as they are cached."""
+    want_f32(qkv, "the fused projection")
+    T = qkv.shape[0]
+    if qkv.shape[1] != heads * dk + kv_heads * (dk + dv):
+        raise KernelError("kv_write: the projection's width does not fit the heads")
+    for t in (v_keep, v_other):
+        if t is not None:
+            want_f32(t, "values handed between layers")
+            if t.shape != (T, kv_heads * dv):
+                raise KernelError("kv_write: values handed between layers must be [T, kv_heads * dv]")
+    if cache is not None and (cache.dtype != q_out.dtype or cache.shape[1] != 1 or cache.shape[2] != kv_heads
+                              or cache.shape[4] != dk + dv):
+        raise KernelError("kv_write: the cache does not fit the heads")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_bias_kv_write(
+        ptr(qkv), ptr(q_out), ptr(cache), c_int(code(q_out.dtype)), ptr(v_keep), ptr(v_other), c_float(mix),
+        ptr(positions), ptr(seq_of_token), ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(T),
+        c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_int(page_table.shape[0]),
+        c_int(cache.shape[0] if cache is not None else 0), stream()))
+
+
+def runs_usable(dk: int, dv: int, page_size: int) -> bool:
+    """Whether the kernel for runs of new tokens takes these sizes."""
+    return False
+
+
+def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:
+    """Ranges the visible keys of a (token, head) are cut into: a step of few tokens is cut until a block has about
+    64 keys or the launch fills the GPU three times over; prompts are not cut.  The ranges are joined in range
+    order, so a launch shape always gives the same bits; logits agree across shapes to rounding."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    return int(max(1, min(64, longest // 64, (12 * sms) // max(1, n_tokens * heads))))
+
+
+def attention(q: torch.Tensor, cache: torch.Tensor, bias: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+              positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
+              window: int, keep_first: int, scale: float, out: torch.Tensor, heads: int, kv_heads: int, dk: int,
+              dv: int, n_splits: int = 1) -> torch.Tensor:
+    """Every (token, head) on its own over its sequence's cache.  q [T, heads, dk]; out [T, heads * dv]; bias float32
+    [far + 1, heads], row min(distance, far) added to the scaled score (None: no bias); sink float32 [heads]: exp(sink)
+    joins the softmax's denominator (None: an ordinary softmax); window 0: every earlier position is seen, else the
+    last `window` and the first `keep_first`."""
+    T = q.shape[0]
+    want_int32(positions, "positions")
+    want_int32(page_table, "page table")
+    far = 0
+    if bias is not None:
+        want_f32(bias, "the distance bias")
+        if bias.dim() != 2 or bias.shape[1] != heads:
+            raise KernelError("attention: the distance bias must be [distances, heads]")
+        far = bias.shape[0] - 1
+    if sink is not None:
+        want_f32(sink, "the sink")
+    partial = torch.empty(T * heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_bias_attention(
+        ptr(q), ptr(cache), c_int(code(q.dtype)), ptr(bias), c_int(far), ptr(sink), ptr(positions), ptr(seq_of_token),
+        ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale),
+        ptr(out), ptr(partial), c_int(n_splits), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+        c_int(page_table.shape[0]), c_int(cache.shape[0]), stream()), kernels=2 if n_splits > 1 else 1)
+    return out

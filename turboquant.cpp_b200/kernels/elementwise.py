@@ -67,6 +67,31 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class Glu:
+    """A gated activation: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(slope * g) * (u + offset).
+    limit 0 means no caps; (0, 1, 0) is silu(gate) * up."""
+
+    def __init__(self, limit: float = 0.0, slope: float = 1.0, offset: float = 0.0):
+        if limit < 0.0:
+            raise ValueError(f"a gated activation's caps must not be negative, got {limit}")
+        self.limit, self.slope, self.offset = float(limit), float(slope), float(offset)
+
+    def __repr__(self):
+        return f"Glu(limit={self.limit}, slope={self.slope}, offset={self.offset})"
+
+
+SILU_GLU = Glu()
+
+
+def glu_mul(gate_up: torch.Tensor, out: torch.Tensor, glu: Glu = SILU_GLU) -> torch.Tensor:
+    """out[t, i] = glu(gate_up[t, i], gate_up[t, I + i]), computed in float32."""
+    T, I = out.shape
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_glu_mul(ptr(gate_up), c_int(code(gate_up.dtype)), ptr(out), c_int(code(out.dtype)),
+                               c_int(T), c_int(I), c_float(glu.limit), c_float(glu.slope), c_float(glu.offset), stream()))
+    return out
+
+
 def gather_rows(src: torch.Tensor, index: torch.Tensor, divisor: int, out: torch.Tensor) -> torch.Tensor:
     """out[r] = src[index[r] // divisor]."""
     want_int32(index, "index")

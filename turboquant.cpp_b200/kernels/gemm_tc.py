@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import os
-from ctypes import c_int
+from ctypes import c_float, c_int
 from typing import Dict, Optional
 
 import torch
@@ -129,7 +129,7 @@ _NO_PAIRS = os.environ.get("TQ_NO_PAIRS", "") not in ("", "0")
 
 def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Optional[ExpertLayout],
             token_tile: int, pair: Optional[bool] = None, status: Optional[torch.Tensor] = None,
-            sm_share: int = 0, k_splits: int = 1, early_weights: bool = False) -> torch.Tensor:
+            sm_share: int = 0, k_splits: int = 1, early_weights: bool = False, glu=None) -> torch.Tensor:
     """x [R, K] bf16; w: packed weights of G groups; out [R, N] bf16 or fp32 (with w.swiglu:
     silu(x.Wg) * (x.Wu)).  layout: expert-sorted tiles of `token_tile` rows (None: one group).
     pair: run on pairs of CTAs (default: for wide token tiles, unless TQ_NO_PAIRS=1).  status: the int32 the
@@ -138,7 +138,8 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
     k_splits > 1: out is [k_splits, R, N] float32; slice s holds the partial sums over the s-th share of K (see
     k_splits_for) and the caller adds the slices up in order.  early_weights: the caller vouches that the weights
     and the layout were final before the kernel ahead of this one in the stream started (a down projection behind
-    its gate/up product); the kernel then starts streaming weights while that kernel still runs."""
+    its gate/up product); the kernel then starts streaming weights while that kernel still runs.
+    glu: the gated activation of a SwiGLU-packed product (kernels.elementwise.Glu; default silu(gate) * up)."""
     if pair is None:
         pair = token_tile >= PAIR_MIN_TILE and not _NO_PAIRS
     if not usable(x, w):
@@ -161,8 +162,14 @@ def gemm_tc(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: Option
         ptr(lo.n_tiles) if lo else None, c_int(lo.max_tiles if lo else 0), c_int(token_tile),
         c_int(R), c_int(N), c_int(K), c_int(w.groups), c_int(1 if w.swiglu else 0), c_int(1 if pair else 0),
         ptr(status if status is not None else status_word(x.device)), c_int(int(sm_share)), c_int(int(k_splits)),
-        c_int(1 if early_weights else 0), stream()))
+        c_int(1 if early_weights else 0), *_glu_args(glu), stream()))
     return out
+
+
+def _glu_args(glu):
+    from .elementwise import SILU_GLU
+    g = glu if glu is not None else SILU_GLU
+    return c_float(g.limit), c_float(g.slope), c_float(g.offset)
 
 
 DUAL_CALLS = 0       # launches of two products so far (tests read it)
@@ -170,13 +177,14 @@ DUAL_CALLS = 0       # launches of two products so far (tests read it)
 
 def gemm_tc_dual(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: ExpertLayout,
                  x2: torch.Tensor, w2: PackedWeights, out2: torch.Tensor, token_tile: int,
-                 status: Optional[torch.Tensor] = None, second_first: bool = False) -> None:
+                 status: Optional[torch.Tensor] = None, second_first: bool = False, glu=None, glu2=None) -> None:
     """Two products in one launch on pairs of CTAs: out = x . w over the layout's groups (as gemm_tc), and
     out2 = x2 . w2 over one group with token tiles of `token_tile` (128 or 256) consecutive rows.  Both SwiGLU (bf16
     results) or both plain (float32 results).  The persistent CTAs walk both products' tiles in one sequence, the
     second product's spread evenly among the first's (or first, with second_first): a product bound by the tensor
     cores beside one bound by its weight stream, where two launches would run one after the other.  The results
-    are those of two separate launches with the same token tile, bit for bit."""
+    are those of two separate launches with the same token tile, bit for bit.  glu, glu2: the two products' gated
+    activations (SwiGLU launches); they may differ in their caps only."""
     if not (usable(x, w) and usable(x2, w2)):
         raise KernelError("gemm_tc_dual: needs bfloat16 activations with K a multiple of 8 and weights packed for this K")
     if w.swiglu != w2.swiglu or out.dtype != out2.dtype:
@@ -194,4 +202,5 @@ def gemm_tc_dual(x: torch.Tensor, w: PackedWeights, out: torch.Tensor, layout: E
         ptr(layout.n_tiles), c_int(layout.max_tiles), c_int(x.shape[0]), c_int(w.n), c_int(w.k), c_int(w.groups),
         ptr(x2), ptr(w2.data), ptr(out2), c_int(x2.shape[0]), c_int(w2.n), c_int(w2.k), c_int(code(out.dtype)),
         c_int(token_tile), c_int(1 if w.swiglu else 0),
-        ptr(status if status is not None else status_word(x.device)), c_int(1 if second_first else 0), stream()))
+        ptr(status if status is not None else status_word(x.device)), c_int(1 if second_first else 0),
+        *_glu_args(glu), c_float(_glu_args(glu2 if glu2 is not None else glu)[0].value), stream()))

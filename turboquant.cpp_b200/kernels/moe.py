@@ -1,7 +1,7 @@
 """Mixture-of-experts kernels (csrc/moe.cu): router, expert-sorted layout, grouped GEMM, combine."""
 from __future__ import annotations
 
-from ctypes import c_int
+from ctypes import c_float, c_int
 from typing import Optional
 
 import torch
@@ -47,6 +47,43 @@ def router_select(logits: torch.Tensor, top_k: int, renorm: bool, ids: torch.Ten
     lib = load_kernel(_LIB)
     check(_LIB, lib.tq_router_select(ptr(logits), ptr(ids), ptr(weights), ptr(shared_scale), c_int(T), c_int(E1 - 1),
                                      c_int(top_k), c_int(1 if renorm else 0), stream()))
+
+
+def router_logits(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor],
+                  logits: torch.Tensor) -> torch.Tensor:
+    """logits [T, E + 1] float32: x . w_router rows, and in column E x . w_shared_gate (if given), summed in float32."""
+    T, H = x.shape
+    E = w_router.shape[0]
+    want_f32(logits, "router logits")
+    if w_shared_gate is not None and w_shared_gate.dtype != w_router.dtype:
+        w_shared_gate = w_shared_gate.to(w_router.dtype)
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_router_logits(ptr(x), c_int(code(x.dtype)), ptr(w_router), ptr(w_shared_gate),
+                                     c_int(code(w_router.dtype)), ptr(logits), c_int(T), c_int(H), c_int(E), stream()))
+    return logits
+
+
+def router_select_corrected(logits: torch.Tensor, correction: Optional[torch.Tensor], top_k: int, renorm: bool,
+                            floor: float, n_groups: int, keep_groups: int, ids: torch.Tensor, weights: torch.Tensor,
+                            shared_scale: Optional[torch.Tensor]) -> None:
+    """Selection on float32 logits [T, E + 1] with a correction of the choice and groups of experts: scores are the
+    softmax over all experts; the choice looks at score + correction [E] (float32, or None); with n_groups > 1 only
+    experts of the keep_groups groups (of E / n_groups neighbours) with the largest such value can be chosen; the
+    weights are the chosen experts' scores, divided by (their sum + floor) if renorm."""
+    want_f32(logits, "router logits")
+    want_int32(ids, "expert ids")
+    want_f32(weights, "expert weights")
+    if correction is not None:
+        want_f32(correction, "the choice's correction")
+    T, E1 = logits.shape
+    E = E1 - 1
+    choice = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    group_best = torch.empty((T, n_groups), dtype=torch.float32, device=logits.device) if n_groups > 1 else None
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_router_select_corrected(ptr(logits), ptr(correction), ptr(choice), ptr(group_best), ptr(ids),
+                                               ptr(weights), ptr(shared_scale), c_int(T), c_int(E), c_int(top_k),
+                                               c_int(1 if renorm else 0), c_float(floor), c_int(n_groups),
+                                               c_int(keep_groups), stream()))
 
 
 def max_tiles(n_pairs: int, n_experts: int, tile_rows: int) -> int:
@@ -130,11 +167,12 @@ def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Optional[ExpertLayout],
-                 swiglu: bool, few_rows: bool = False) -> torch.Tensor:
+                 swiglu: bool, few_rows: bool = False, glu=None) -> torch.Tensor:
     """Exact (CUDA-core, fp32 accumulation) grouped product.  a [R, K]; w [G, Nw, K] with Nw = N,
     or 2N when swiglu (gate rows, then up rows); out [R, N].  layout None: one group (G = 1).
     few_rows: the tiles hold a few rows each (a decode step): the kernel that streams the weights once per eight
-    rows of a tile instead of the tiled one (any number of rows is right, many are slow)."""
+    rows of a tile instead of the tiled one (any number of rows is right, many are slow).
+    glu: the gated activation of a swiglu product (kernels.elementwise.Glu; default silu(gate) * up)."""
     R, K = a.shape
     N = out.shape[1]
     if w.dim() == 2:
@@ -143,12 +181,14 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, layout: Op
     assert layout is not None or w.shape[0] == 1
     lib = load_kernel(_LIB)
     lo = layout
+    from .elementwise import SILU_GLU
+    g = glu if glu is not None else SILU_GLU
     check(_LIB, lib.tq_grouped_gemm(
         ptr(a), c_int(code(a.dtype)), ptr(w), c_int(code(w.dtype)), ptr(out), c_int(code(out.dtype)),
         ptr(lo.tile_expert) if lo else None, ptr(lo.tile_row0) if lo else None,
         ptr(lo.tile_count) if lo else None, ptr(lo.n_tiles) if lo else None,
         c_int(lo.max_tiles if lo else 0), c_int(R), c_int(N), c_int(K), c_int(1 if swiglu else 0),
-        c_int(1 if few_rows else 0), stream()))
+        c_int(1 if few_rows else 0), c_float(g.limit), c_float(g.slope), c_float(g.offset), stream()))
     return out
 
 

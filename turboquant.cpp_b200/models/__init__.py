@@ -2,3 +2,4 @@
 from .decoder import DecoderModel, Embedding, LMHead, PairEmbedding, ScheduleEntry
 from .qwen2_moe import Qwen2MoeModel
 from .nuforax import NuforaxModel
+from .lumevik import LumevikModel

@@ -203,6 +203,7 @@ class DecoderModel:
         """Runs the step's tokens through the schedule; float32 logits [n_want, vocab] (None if
         nothing is wanted)."""
         x = self.embedding.embed(ctx) if hasattr(self.embedding, "embed") else self.embedding.forward(ctx.tokens)
+        ctx.carry = {}                   # what layers hand to later layers lives for one step
         pending = None
         dump = ctx.debug.get("layer_sums") if ctx.debug is not None else None
         keep = ctx.debug.get("layer_streams") if ctx.debug is not None else None     # tests: the stream after each layer

@@ -7,7 +7,8 @@ from .norm import RMSNorm
 from .rotary import RotaryEncoding, ScaledRotaryEncoding
 from .attention import AttentionMixer
 from .latent_attention import LatentAttentionMixer
+from .bias_attention import BiasedWindowAttentionMixer
 from .ssm import Mamba2Mixer
-from .dense_ffn import SwiGLUFeedForward, ReluSquaredFeedForward
+from .dense_ffn import SwiGLUFeedForward, ReluSquaredFeedForward, GluFeedForward
 from .moe_ffn import MoEFeedForward
 from .block import PreNormBlock, PostNormBlock

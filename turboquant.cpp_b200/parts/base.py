@@ -45,11 +45,12 @@ from ..weights.loader import WeightSpec, WeightStore
 class KVNeed:
     """What a mixer needs from the key/value cache.  Layers with equal needs share a group of
     storage.  window = 0: every position is kept; window = w: positions older than the last w may
-    be given back."""
+    be given back, except a sequence's first keep_first positions, which stay."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2          # tensors kept per position: 2 (keys and values), or 1 (one row that serves as both)
+    keep_first: int = 0      # positions at a sequence's start that a windowed group never gives back
 
 
 @dataclass(frozen=True)
@@ -94,6 +95,9 @@ class StepContext:
     debug: Optional[Dict[str, Any]] = None      # tests: parts may record what they decided
     status: Optional[torch.Tensor] = None       # int32 [1]: kernels with bounded waits report here when one ran out
     embed_state: Optional[torch.Tensor] = None  # [max_slots, *shape]: the embedding's per-sequence state, if it keeps one
+    # what a layer hands to later layers of the same step (the model empties it when a step starts): tensors over
+    # the step's tokens under names the parts agree on, e.g. the values that later layers mix into their own
+    carry: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 class Part:

@@ -1,0 +1,147 @@
+"""Attention with a learned distance bias, a window that keeps a sequence's first positions, a sink in the softmax
+and values mixed across layers.  No rotation: positions enter through the bias and the mask only.
+
+With h the mixer's input, H query heads on G key/value heads (head a reads a // (H / G)), key size dk, value size dv:
+
+    q = W_q h, k = W_k h, v = W_v h                                    (one fused product, float32 result)
+    score(i, j) = q_i . k_j * scale + rel[bucket(i - j)][a]
+    bucket(n)   = n                                                    for n < B / 2           (B rows in rel)
+                = min(B - 1, B/2 + floor(ln(n / (B/2)) / ln(far / (B/2)) * (B - B/2)))   otherwise
+    i sees j    iff j <= i and (i - j < window or j < keep_first)
+    p_j         = exp(score_j) / (1 + sum of exp(score_j) over the visible j)
+    out_i       = W_o concat_a sum_j p_j v_j
+
+The bucket depends on the distance alone, so the table is spread out per distance once, when the weights are bound
+(distances from `far` on share the last row), and the kernels add row min(i - j, far).  The one in the denominator
+is a sink of score 0: the kernels take a sink per head, here zeros.  Value mixing (`mix_values`): the first mixer of
+a model that mixes keeps its values under a name in the step's `carry`; every later one turns its own into
+(1 - lambda) v + lambda v_first before they are cached, lambda being the layer's scalar tensor `vmix`.
+A position's cache row is [k | v] per key/value head (one plane).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..kernels import bias_attention as KB
+from ..kernels.linear import linear
+from ..weights.loader import WeightSpec, WeightStore
+from .base import KVNeed, LayerCache, Mixer, StepContext, register_mixer
+
+
+def distance_buckets(rows: int, far: int) -> List[int]:
+    """bucket(n) for n = 0 .. far (every distance beyond `far` falls into the last row, as `far` itself does)."""
+    half = rows // 2
+    out = []
+    for n in range(far + 1):
+        if n < half:
+            out.append(n)
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
+
+
+class BiasedWindowAttentionMixer(Mixer):
+    RUNS_MIN = 16             # steps whose longest run of new tokens is at least this take the kernel for runs
+
+    def __init__(self, prefix: str, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int = 0, keep_first: int = 0, bias_rows: int = 0, bias_far: int = 0, sink: bool = True,
+                 mix_values: Optional[str] = None, mix_first: bool = False):
+        """bias_rows: rows of the bias table `rel` (0: no bias; -1: as many as the stored tensor has); bias_far: the
+        distance from which all share the last row.  mix_values: the name under which the model's mixing layers share values in a step's carry (None: this
+        layer does not mix); mix_first: this layer is the one that provides them."""
+        if heads < 1 or kv_heads < 1 or heads % kv_heads:
+            raise ValueError(f"attention '{prefix}': {heads} heads are not a multiple of {kv_heads} key/value heads")
+        if not (1 <= dim <= KB.MAX_DIM and 1 <= vdim <= KB.MAX_DIM):
+            raise ValueError(f"attention '{prefix}': key size {dim} and value size {vdim} must be in 1..{KB.MAX_DIM}")
+        if window < 0 or keep_first < 0:
+            raise ValueError(f"attention '{prefix}': negative window {window} or kept positions {keep_first}")
+        if bias_rows > 0:
+            self._check_bias(prefix, bias_rows, bias_far)
+        self.prefix, self.hidden = prefix, int(hidden)
+        self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.window, self.keep_first = float(scale), int(window), int(keep_first) if window else 0
+        self.bias_rows, self.bias_far, self.has_sink = int(bias_rows), int(bias_far), bool(sink)
+        self.mix_values, self.mix_first = mix_values, bool(mix_first)
+        self.q_size, self.k_size, self.v_size = heads * dim, kv_heads * dim, kv_heads * vdim
+        self.w_qkv = self.w_o = self.bias = self.sink = None
+        self.mix = 0.0
+
+    @staticmethod
+    def _check_bias(prefix: str, rows: int, far: int) -> None:
+        if rows < 2 or far <= rows // 2:
+            raise ValueError(f"attention '{prefix}': a bias table of {rows} rows needs a far distance beyond "
+                             f"{rows // 2}, got {far}")
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p, W = self.prefix, self.hidden
+        specs = [WeightSpec(p + "q", (self.q_size, W)), WeightSpec(p + "k", (self.k_size, W)),
+                 WeightSpec(p + "v", (self.v_size, W)), WeightSpec(p + "o", (W, self.heads * self.vdim))]
+        if self.bias_rows:
+            specs.append(WeightSpec(p + "rel", (self.bias_rows, self.heads)))
+        if self.mix_values is not None:
+            specs.append(WeightSpec(p + "vmix", ()))
+        return specs
+
+    def bind(self, store: WeightStore) -> None:
+        p = self.prefix
+        ws = [store.take(p + n) for n in "qkv"]
+        dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()      # one product for q, k and v
+        self.w_o = store.get(p + "o")
+        if self.bias_rows:
+            rel = store.get(p + "rel").float()
+            self._check_bias(p, rel.shape[0], self.bias_far)
+            self.bias_rows = rel.shape[0]
+            index = torch.tensor(distance_buckets(rel.shape[0], self.bias_far), dtype=torch.long, device=rel.device)
+            self.bias = rel[index].contiguous()                                  # [far + 1, heads], a row per distance
+        if self.has_sink:
+            self.sink = torch.zeros(self.heads, dtype=torch.float32, device=store.device)
+        if self.mix_values is not None:
+            self.mix = float(store.get(p + "vmix").float().item())
+
+    def kernels(self) -> List[str]:
+        return ["bias_attention"]
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(self.kv_heads, self.dim + self.vdim, self.window, planes=1, keep_first=self.keep_first)
+
+    def step_work(self, n_tokens, kv_tokens):
+        wb = lambda w: 0 if w is None else w.numel() * w.element_size()
+        proj = self.hidden * (self.q_size + self.k_size + self.v_size) + self.heads * self.vdim * self.hidden
+        el = 2 if getattr(self, "run_dtype", None) == torch.bfloat16 else 4
+        seen = min(kv_tokens, n_tokens * (self.window + self.keep_first)) if self.window else kv_tokens
+        return {"matmul": (wb(self.w_qkv) + wb(self.w_o), 2.0 * n_tokens * proj),
+                "attn": (float((self.k_size + self.v_size) * el * seen), 2.0 * self.heads * (self.dim + self.vdim) * seen)}
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        T, act, dev = xn.shape[0], ctx.act_dtype, xn.device
+        qkv = linear(xn, self.w_qkv, out_dtype=torch.float32)
+        q = torch.empty((T, self.heads, self.dim), dtype=act, device=dev)
+        keep = other = None
+        if self.mix_values is not None:
+            if self.mix_first:
+                keep = ctx.carry[self.mix_values] = torch.empty((T, self.v_size), dtype=torch.float32, device=dev)
+            else:
+                other = ctx.carry.get(self.mix_values)
+                if other is None or other.shape != (T, self.v_size):
+                    raise RuntimeError(f"attention '{self.prefix}': no values of {self.v_size} elements to mix with "
+                                       f"were handed on by an earlier layer of this step")
+        KB.kv_write(qkv, q, cache.kv if cache.writes else None, keep, other, self.mix, ctx.positions, ctx.seq_of_token,
+                    cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
+        o = torch.empty((T, self.heads * self.vdim), dtype=act, device=dev)
+        if ctx.max_q_len >= self.RUNS_MIN and KB.runs_usable(self.dim, self.vdim, cache.page_size):
+            KB.attention_runs(q, cache.kv, self.bias, self.sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table,
+                              cache.page_size, self.window, self.keep_first, self.scale, o, ctx.n_seqs, ctx.max_q_len,
+                              self.heads, self.kv_heads, self.dim, self.vdim)
+        else:
+            longest = min(self.window + self.keep_first, ctx.max_kv_len) if self.window else ctx.max_kv_len
+            KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
+                         cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
+                         self.dim, self.vdim, n_splits=KB.splits_for(T, self.heads, longest, dev))
+        return linear(o, self.w_o, out_dtype=torch.float32)
+
+
+register_mixer("window_bias_attention", BiasedWindowAttentionMixer)

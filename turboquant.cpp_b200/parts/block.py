@@ -15,11 +15,15 @@ from .base import Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, StateNeed
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+    """The feed-forward (and its norm) may be absent: the mixer's output is then what the block leaves open."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn: Optional[FeedForward] = None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def cache_need(self) -> Optional[KVNeed]:
         return self.mixer.cache_need()
@@ -28,7 +32,7 @@ class PreNormBlock(Block):
         return self.mixer.state_need()
 
     def capturable(self) -> bool:
-        return self.mixer.capturable() and self.ffn.capturable()
+        return self.mixer.capturable() and (self.ffn is None or self.ffn.capturable())
 
     def weight_specs(self) -> List[WeightSpec]:
         return [s for p in self.parts() for s in p.weight_specs()]
@@ -47,6 +51,8 @@ class PreNormBlock(Block):
         else:
             xn = self.mixer_norm.add_forward(x, pending, ctx.act_dtype)
         y = self.mixer.forward(xn, ctx, cache)
+        if self.ffn is None:
+            return x, y
         xn = self.ffn_norm.add_forward(x, y, ctx.act_dtype)
         return x, self.ffn.forward(xn, ctx)
 

@@ -48,6 +48,48 @@ class SwiGLUFeedForward(FeedForward):
 register_feed_forward("swiglu", SwiGLUFeedForward)
 
 
+class GluFeedForward(FeedForward):
+    """down(glu(gate x, up x)) with a gated activation given by its constants (kernels.elementwise.Glu: caps on gate
+    and up, the slope inside the sigmoid, an offset on up); the tensors' names are parameters.  Gate and up are
+    one fused product whose float32 result the activation reads."""
+
+    def __init__(self, prefix: str, hidden: int, intermediate: int, glu: K.Glu = K.SILU_GLU, gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down"):
+        if hidden < 1 or intermediate < 1:
+            raise ValueError(f"feed-forward '{prefix}': sizes must be positive, got {hidden}, {intermediate}")
+        self.prefix, self.hidden, self.intermediate, self.glu = prefix, int(hidden), int(intermediate), glu
+        self.names = (gate_name, up_name, down_name)
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        p, H, I = self.prefix, self.hidden, self.intermediate
+        return [WeightSpec(p + self.names[0], (I, H)), WeightSpec(p + self.names[1], (I, H)),
+                WeightSpec(p + self.names[2], (H, I))]
+
+    def bind(self, store: WeightStore) -> None:
+        p = self.prefix
+        g, u = store.take(p + self.names[0]), store.take(p + self.names[1])
+        dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.w_down = store.get(p + self.names[2])
+
+    def kernels(self) -> List[str]:
+        return ["elementwise"]
+
+    def step_work(self, n_tokens, kv_tokens):
+        wb = lambda w: 0 if w is None else w.numel() * w.element_size()
+        return {"matmul": (wb(self.w_gate_up) + wb(self.w_down), 6.0 * n_tokens * self.hidden * self.intermediate)}
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gu = linear(xn, self.w_gate_up, out_dtype=torch.float32)
+        h = torch.empty((xn.shape[0], self.intermediate), dtype=ctx.act_dtype, device=xn.device)
+        K.glu_mul(gu, h, self.glu)
+        return linear(h, self.w_down, out_dtype=torch.float32)
+
+
+register_feed_forward("glu", GluFeedForward)
+
+
 class ReluSquaredFeedForward(FeedForward):
     """down(relu(up x)^2): one product up, the square of relu, one product down."""
 

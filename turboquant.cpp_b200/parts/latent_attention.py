@@ -13,8 +13,10 @@ With h the mixer's input, H heads, per head `dim` plain and `rot_dim` rotated qu
 Only [c | kr] is cached.  The products with W_uk and W_uv are moved to the query's side: q~_a = W_uk,a^T q_plain
 meets c directly, the softmax-weighted sum of the c_j is taken first and W_uv,a applied to it, so one cached row
 serves all heads as key and value, in prompts and in decoding alike.  Options: a window (position i sees j with
-0 <= i - j < window), a learned sink per head in the softmax's denominator, and reading the rows another layer
-cached (the layer then has no W_dkv).
+0 <= i - j < window), a learned sink per head in the softmax's denominator, reading the rows another layer
+cached (the layer then has no W_dkv), and queries that go through a latent of their own:
+
+    c_q = rms(W_dq h) * w_q,   q = W_uq c_q        (q_rank > 0; tensors dq, dq.norm, uq instead of q)
 """
 from __future__ import annotations
 
@@ -22,6 +24,7 @@ from typing import List, Optional
 
 import torch
 
+from ..kernels import elementwise as KE
 from ..kernels import latent_attention as KL
 from ..kernels.linear import batched_linear, linear, product
 from ..weights.loader import WeightSpec, WeightStore
@@ -34,12 +37,12 @@ class LatentAttentionMixer(Mixer):
 
     def __init__(self, prefix: str, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  scale: float, eps: float, window: int = 0, position=None, own_cache: bool = True,
-                 keep_window: Optional[int] = None, sink: bool = True):
+                 keep_window: Optional[int] = None, sink: bool = True, q_rank: int = 0):
         """position: an encoding with `freq` and `mag` (parts.rotary.ScaledRotaryEncoding) over at most rot_dim
         dimensions, or None.  own_cache False: the layer has no latent projection and reads the rows of the
         schedule entry its own entry names.  keep_window: how long the cache keeps rows (0: all); a layer whose
         rows are read by layers with other windows must keep them for the widest."""
-        if heads < 1 or dim < 0 or rot_dim < 0 or dim + rot_dim < 1 or vdim < 1 or kv_rank < 1:
+        if heads < 1 or dim < 0 or rot_dim < 0 or dim + rot_dim < 1 or vdim < 1 or kv_rank < 1 or q_rank < 0:
             raise ValueError(f"latent attention '{prefix}': bad sizes")
         if kv_rank + rot_dim > KL.MAX_ROW:
             raise ValueError(f"latent attention '{prefix}': kv_rank + rot_dim = {kv_rank + rot_dim} exceeds {KL.MAX_ROW}")
@@ -53,11 +56,19 @@ class LatentAttentionMixer(Mixer):
         self.position, self.own_cache, self.has_sink = position, bool(own_cache), bool(sink)
         self.keep_window = self.window if keep_window is None else int(keep_window)
         self.q_dim = self.dim + self.rot_dim
+        self.q_rank = int(q_rank)            # 0: queries straight from the input
+        self.w_dq = self.w_qnorm = None
         self.w_q = self.w_dkv = self.w_norm = self.w_uk = self.w_uv_t = self.w_o = self.sink = None
 
     def weight_specs(self) -> List[WeightSpec]:
         p, H = self.prefix, self.heads
-        specs = [WeightSpec(p + "q", (H * self.q_dim, self.hidden)), WeightSpec(p + "uk", (H * self.dim, self.kv_rank)),
+        if self.q_rank:
+            specs = [WeightSpec(p + "dq", (self.q_rank, self.hidden)),
+                     WeightSpec(p + "dq.norm", (self.q_rank,), init="one_plus_normal"),
+                     WeightSpec(p + "uq", (H * self.q_dim, self.q_rank))]
+        else:
+            specs = [WeightSpec(p + "q", (H * self.q_dim, self.hidden))]
+        specs += [WeightSpec(p + "uk", (H * self.dim, self.kv_rank)),
                  WeightSpec(p + "uv", (H * self.vdim, self.kv_rank)), WeightSpec(p + "o", (self.hidden, H * self.vdim))]
         if self.own_cache:
             specs += [WeightSpec(p + "dkv", (self.kv_rank + self.rot_dim, self.hidden)),
@@ -68,7 +79,9 @@ class LatentAttentionMixer(Mixer):
 
     def bind(self, store: WeightStore) -> None:
         p, H = self.prefix, self.heads
-        self.w_q, self.w_o = store.get(p + "q"), store.get(p + "o")
+        self.w_q, self.w_o = store.get(p + ("uq" if self.q_rank else "q")), store.get(p + "o")
+        if self.q_rank:
+            self.w_dq, self.w_qnorm = store.get(p + "dq"), store.get(p + "dq.norm")
         self.w_uk = store.get(p + "uk").view(H, self.dim, self.kv_rank)                       # q_plain [T, dim] @ [dim, R]
         self.w_uv_t = store.get(p + "uv").view(H, self.vdim, self.kv_rank).transpose(1, 2)    # sums [T, R] @ [R, vdim]
         if self.own_cache:
@@ -79,7 +92,7 @@ class LatentAttentionMixer(Mixer):
             self.position.prepare(store.device)
 
     def kernels(self) -> List[str]:
-        return ["latent_attention"]
+        return ["latent_attention"] + (["elementwise"] if self.q_rank else [])
 
     def cache_need(self) -> KVNeed:
         return KVNeed(1, self.kv_rank + self.rot_dim, self.keep_window, planes=1)
@@ -87,17 +100,24 @@ class LatentAttentionMixer(Mixer):
     def step_work(self, n_tokens, kv_tokens):
         wb = lambda w: 0 if w is None else w.numel() * w.element_size()
         H, R = self.heads, self.kv_rank
-        proj = self.hidden * H * self.q_dim + H * self.vdim * self.hidden + H * R * (self.dim + self.vdim)
+        proj = ((self.hidden + H * self.q_dim) * self.q_rank if self.q_rank else self.hidden * H * self.q_dim) \
+            + H * self.vdim * self.hidden + H * R * (self.dim + self.vdim)
         if self.own_cache:
             proj += self.hidden * (R + self.rot_dim)
         el = 2 if getattr(self, "run_dtype", None) == torch.bfloat16 else 4
         seen = min(kv_tokens, n_tokens * self.window) if self.window else kv_tokens
-        return {"matmul": (sum(wb(w) for w in (self.w_q, self.w_dkv, self.w_uk, self.w_uv_t, self.w_o)), 2.0 * n_tokens * proj),
+        return {"matmul": (sum(wb(w) for w in (self.w_q, self.w_dq, self.w_dkv, self.w_uk, self.w_uv_t, self.w_o)), 2.0 * n_tokens * proj),
                 "attn": (float((R + self.rot_dim) * el * seen), 2.0 * H * (2 * R + self.rot_dim) * seen)}
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         T, H, R, act = xn.shape[0], self.heads, self.kv_rank, ctx.act_dtype
-        q = linear(xn, self.w_q, out_dtype=act)                                        # [T, H * (dim + rot_dim)]
+        if self.q_rank:
+            # the queries' latent: projection in float32, RMS norm with its weight, rounded to the activation dtype
+            cq = KE.rmsnorm(linear(xn, self.w_dq, out_dtype=torch.float32), self.w_qnorm, self.eps,
+                            torch.empty((T, self.q_rank), dtype=act, device=xn.device))
+            q = linear(cq, self.w_q, out_dtype=act)
+        else:
+            q = linear(xn, self.w_q, out_dtype=act)                                    # [T, H * (dim + rot_dim)]
         dkv = linear(xn, self.w_dkv, out_dtype=torch.float32) if self.own_cache else None
         freq, mag = (self.position.freq, self.position.mag) if self.position is not None and self.position.dims else (None, 1.0)
         # norm of the latent, the two rotations and the cache write in one launch

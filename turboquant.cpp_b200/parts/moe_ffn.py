@@ -9,6 +9,11 @@
 Tokens are copied into an expert-sorted layout, two grouped products run over it (gate|up with the
 SiLU product fused, then down), and one pass sums each token's k rows and the shared expert in the
 order above.  Router logits, softmax and the weighted sum are fp32 on both paths.
+
+Options other designs use: the experts' gated activation as constants (`glu`, `shared_glu`: caps, slope, offset);
+a correction added to the scores for the choice only (`correction`: a tensor of one number per expert); groups of
+neighbouring experts of which only the `keep_groups` best (by their best corrected score) can be chosen; a floor
+added to the chosen scores' sum before the division (`renorm_floor`); the tensors' names (`names`).
 """
 from __future__ import annotations
 
@@ -65,6 +70,12 @@ def shared_rides_with_routed(n_tokens: int, shared_intermediate: int, sms: int) 
     return units < 4 * (sms // 2)
 
 
+# tensor names below a layer's prefix, as Qwen2 MoE checkpoints have them; {e}: the expert's number
+QWEN_NAMES = {"router": "gate.weight", "expert": "experts.{e}.", "gate": "gate_proj.weight", "up": "up_proj.weight",
+              "down": "down_proj.weight", "shared": "shared_expert.", "shared_gate": "shared_expert_gate.weight",
+              "correction": "gate.e_score_correction_bias"}
+
+
 class MoEFeedForward(FeedForward):
     # steps with at least this many tokens (and too many pairs for the one-launch router) compute router logits on
     # tensor cores (measured on B200 at 64 tokens: +2.4 % on the step at the 57B-A14B sizes, +0.8 % at the A2.7B sizes)
@@ -77,9 +88,22 @@ class MoEFeedForward(FeedForward):
     SHARED_DOWN_SPLIT_RATIO = float(os.environ.get("TQ_SHARED_DOWN_SPLIT_RATIO", "14"))
 
     def __init__(self, prefix: str, hidden: int, n_experts: int, top_k: int, intermediate: int,
-                 norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True):
+                 norm_topk: bool, shared_intermediate: int = 0, shared_gate: bool = True,
+                 glu: KE.Glu = KE.SILU_GLU, shared_glu: Optional[KE.Glu] = None, correction: bool = False,
+                 n_groups: int = 1, keep_groups: int = 1, renorm_floor: float = 0.0, names=None):
         if n_experts < 1 or not 1 <= top_k <= n_experts:
             raise ValueError(f"experts '{prefix}': top-k {top_k} must be in 1..{n_experts}")
+        if n_groups < 1 or n_experts % n_groups or not 1 <= keep_groups <= n_groups \
+                or (n_groups > 1 and keep_groups * (n_experts // n_groups) < top_k):
+            raise ValueError(f"experts '{prefix}': {n_experts} experts in {n_groups} groups of which {keep_groups} are "
+                             f"kept cannot give {top_k} choices")
+        self.glu, self.shared_glu = glu, shared_glu if shared_glu is not None else glu
+        self.has_correction, self.n_groups, self.keep_groups = bool(correction), int(n_groups), int(keep_groups)
+        self.renorm_floor = float(renorm_floor)
+        # the choice needs more than the k largest logits: the selection kernel that knows corrections and groups
+        self.corrected = self.has_correction or self.n_groups > 1 or self.renorm_floor > 0.0
+        self.names = dict(QWEN_NAMES, **(names or {}))
+        self.w_correction = None
         if hidden < 1 or intermediate < 1 or shared_intermediate < 0:
             raise ValueError(f"experts '{prefix}': bad sizes {hidden}, {intermediate}, {shared_intermediate}")
         self.prefix, self.hidden = prefix, int(hidden)
@@ -91,42 +115,45 @@ class MoEFeedForward(FeedForward):
         self.ws13 = self.ws2 = None          # shared expert [1, 2S, H], [1, H, S]
 
     def weight_specs(self) -> List[WeightSpec]:
-        p, H, I, S = self.prefix, self.hidden, self.intermediate, self.shared_intermediate
-        specs = [WeightSpec(p + "gate.weight", (self.n_experts, H))]
+        p, H, I, S, n = self.prefix, self.hidden, self.intermediate, self.shared_intermediate, self.names
+        specs = [WeightSpec(p + n["router"], (self.n_experts, H))]
+        if self.has_correction:
+            specs.append(WeightSpec(p + n["correction"], (self.n_experts,)))
         for e in range(self.n_experts):
-            q = f"{p}experts.{e}."
-            specs += [WeightSpec(q + "gate_proj.weight", (I, H)), WeightSpec(q + "up_proj.weight", (I, H)),
-                      WeightSpec(q + "down_proj.weight", (H, I))]
+            q = p + n["expert"].format(e=e)
+            specs += [WeightSpec(q + n["gate"], (I, H)), WeightSpec(q + n["up"], (I, H)), WeightSpec(q + n["down"], (H, I))]
         if S > 0:
-            q = p + "shared_expert."
-            specs += [WeightSpec(q + "gate_proj.weight", (S, H)), WeightSpec(q + "up_proj.weight", (S, H)),
-                      WeightSpec(q + "down_proj.weight", (H, S))]
+            q = p + n["shared"]
+            specs += [WeightSpec(q + n["gate"], (S, H)), WeightSpec(q + n["up"], (S, H)), WeightSpec(q + n["down"], (H, S))]
             if self.shared_gate:
-                specs.append(WeightSpec(p + "shared_expert_gate.weight", (1, H)))
+                specs.append(WeightSpec(p + n["shared_gate"], (1, H)))
         return specs
 
     def bind(self, store: WeightStore) -> None:
         p, H, I, S, E = self.prefix, self.hidden, self.intermediate, self.shared_intermediate, self.n_experts
-        self.w_router = store.get(p + "gate.weight")
+        nm = self.names
+        self.w_router = store.get(p + nm["router"])
+        if self.has_correction:
+            self.w_correction = store.get(p + nm["correction"]).float().contiguous()
         # a tensor stored in 32 bits stays 32-bit: if any of the experts' tensors is kept in float32, the stacked
         # buffers are float32 (the others widen exactly), never the other way round
-        names = [f"{p}experts.{e}.{n}_proj.weight" for e in range(E) for n in ("gate", "up", "down")]
+        names = [p + nm["expert"].format(e=e) + nm[n] for e in range(E) for n in ("gate", "up", "down")]
         dt = torch.float32 if any(store.kept_dtype_of(n) == torch.float32 for n in names) else store.kept_dtype_of(names[0])
         self.w13 = torch.empty((E, 2 * I, H), dtype=dt, device=store.device)
         self.w2 = torch.empty((E, H, I), dtype=dt, device=store.device)
         for e in range(E):
-            q = f"{p}experts.{e}."
-            self.w13[e, :I].copy_(store.take(q + "gate_proj.weight"))
-            self.w13[e, I:].copy_(store.take(q + "up_proj.weight"))
-            self.w2[e].copy_(store.take(q + "down_proj.weight"))
+            q = p + nm["expert"].format(e=e)
+            self.w13[e, :I].copy_(store.take(q + nm["gate"]))
+            self.w13[e, I:].copy_(store.take(q + nm["up"]))
+            self.w2[e].copy_(store.take(q + nm["down"]))
         if S > 0:
-            q = p + "shared_expert."
-            g, u, d = (store.take(q + n + "_proj.weight") for n in ("gate", "up", "down"))
+            q = p + nm["shared"]
+            g, u, d = (store.take(q + nm[n]) for n in ("gate", "up", "down"))
             sdt = torch.float32 if torch.float32 in (g.dtype, u.dtype, d.dtype) else g.dtype
             self.ws13 = torch.cat([g.to(sdt), u.to(sdt)], dim=0).unsqueeze(0).contiguous()
             self.ws2 = d.to(sdt).unsqueeze(0).contiguous()
             if self.shared_gate:
-                self.w_shared_gate = store.get(p + "shared_expert_gate.weight")
+                self.w_shared_gate = store.get(p + nm["shared_gate"])
         if store.run_dtype == torch.bfloat16 and H % 8 == 0 and self.w_router.dtype == torch.bfloat16:
             rows = [self.w_router]
             if self.w_shared_gate is not None:
@@ -171,17 +198,17 @@ class MoEFeedForward(FeedForward):
     EXACT_SHARED_ROWS = 2        # rows of the shared expert that the exact weight-stream kernel takes in one pass
     EXACT_FEW_ROWS = int(os.environ.get("TQ_EXACT_FEW_ROWS", "64"))      # steps of up to this many tokens take the exact kernels' weight-stream form
 
-    def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False):
+    def _product(self, x, w, out, layout, swiglu, token_tile, status=None, early=False, glu=None):
         """Tensor cores for weights packed at load time (bfloat16, 16-byte rows), the exact CUDA-core
         kernel otherwise.  early: this is a down projection right behind its gate/up product in the stream: its
         weights and the layout were there before that product started, so it may stream weights while that runs."""
         if isinstance(w, KT.PackedWeights):
-            return KT.gemm_tc(x, w, out, layout, token_tile, status=status, early_weights=early and self.EARLY_WEIGHTS)
+            return KT.gemm_tc(x, w, out, layout, token_tile, status=status, early_weights=early and self.EARLY_WEIGHTS, glu=glu)
         # the exact kernels: tiles of a few rows (decode steps) stream the weights; a group's tile holds at most the
         # step's tokens, and the one-group product (the shared expert) all of them
         rows = x.shape[0]
         few = rows <= self.EXACT_FEW_ROWS if layout is None else rows <= self.EXACT_FEW_ROWS * self.top_k
-        return KM.grouped_gemm(x, w, out, layout, swiglu, few_rows=few)
+        return KM.grouped_gemm(x, w, out, layout, swiglu, few_rows=few, glu=glu)
 
     def _joint_launches(self, T: int, tile: int, act, dev) -> bool:
         """Whether the shared expert's two products ride in the routed experts' launches, their tiles ahead of the
@@ -219,7 +246,7 @@ class MoEFeedForward(FeedForward):
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
-        small = KM.router_small_pays(T, k, self.n_experts, H)
+        small = KM.router_small_pays(T, k, self.n_experts, H) and not self.corrected
         # Decode steps whose pairs reach the number of experts (most experts are read: the routed products are several
         # times the shared expert's): the router first, alone on the GPU, then the shared expert beside the routed
         # ones with its down projection's K shared out.  With fewer pairs the shared expert starts first and the
@@ -241,10 +268,10 @@ class MoEFeedForward(FeedForward):
                     # one pass of the exact weight-stream kernel holds: the shared expert is a dense feed-forward, and
                     # the library's products serve it as they serve the dense layers
                     gu = linear(xn, self.ws13[0], out_dtype=torch.float32)
-                    KE.silu_mul(gu, hs)
+                    KE.glu_mul(gu, hs, self.shared_glu)
                     y_shared = linear(hs, self.ws2[0], out_dtype=torch.float32)
                     return
-                self._product(xn, self.ws13, hs, None, True, stile, ctx.status)
+                self._product(xn, self.ws13, hs, None, True, stile, ctx.status, glu=self.shared_glu)
                 splits = 1
                 if isinstance(self.ws2, KT.PackedWeights):
                     splits = shared_down_shares(T, self.n_experts, k, self.intermediate, S, H, stile, KA_resident(dev),
@@ -269,7 +296,16 @@ class MoEFeedForward(FeedForward):
                 # are exact in fp32 and the sum is fp32), then the selection kernel
                 logits = torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev)
                 KT.gemm_tc(xn, self.w_router_packed, logits, None, KT.token_tile_for(T, 1), status=ctx.status)
-                KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
+                if self.corrected:
+                    KM.router_select_corrected(logits, self.w_correction, k, self.norm_topk, self.renorm_floor,
+                                               self.n_groups, self.keep_groups, ids, wts, scale)
+                else:
+                    KM.router_select(logits, k, self.norm_topk, ids, wts, scale)
+            elif self.corrected:
+                logits = KM.router_logits(xn, self.w_router, self.w_shared_gate,
+                                          torch.empty((T, self.n_experts + 1), dtype=torch.float32, device=dev))
+                KM.router_select_corrected(logits, self.w_correction, k, self.norm_topk, self.renorm_floor,
+                                           self.n_groups, self.keep_groups, ids, wts, scale)
             else:
                 KM.router_topk(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale)
             KM.moe_align(ids, layout)
@@ -287,10 +323,11 @@ class MoEFeedForward(FeedForward):
             first = self.SHARED_IN_ROUTED_LAUNCH != "spread"
             hs = torch.empty((T, self.shared_intermediate), dtype=act, device=dev)
             y_shared = torch.empty((T, H), dtype=torch.float32, device=dev)
-            KT.gemm_tc_dual(x_rows, self.w13, h_rows, layout, xn, self.ws13, hs, tile, ctx.status, first)
+            KT.gemm_tc_dual(x_rows, self.w13, h_rows, layout, xn, self.ws13, hs, tile, ctx.status, first,
+                            glu=self.glu, glu2=self.shared_glu)
             KT.gemm_tc_dual(h_rows, self.w2, y_rows, layout, hs, self.ws2, y_shared, tile, ctx.status, first)
         else:
-            self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status)
+            self._product(x_rows, self.w13, h_rows, layout, True, tile, ctx.status, glu=self.glu)
             self._product(h_rows, self.w2, y_rows, layout, False, tile, ctx.status, early=True)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)

@@ -12,17 +12,21 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
-    def __init__(self, name: str, size: int, eps: float):
+    def __init__(self, name: str, size: int, eps: float, around_zero: bool = False):
+        """around_zero: the stored weight is the distance from one (y = x / rms * (1 + w)); the sum 1 + w is taken
+        once, when the weights are bound, and kept in float32 (in bfloat16 it would lose the weight's low bits)."""
         if size < 1 or not eps > 0.0:
             raise ValueError(f"RMSNorm '{name}': size {size} and eps {eps} must be positive")
-        self.name, self.size, self.eps = name, int(size), float(eps)
+        self.name, self.size, self.eps, self.around_zero = name, int(size), float(eps), bool(around_zero)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name, (self.size,), init="one_plus_normal")]
+        return [WeightSpec(self.name, (self.size,), init="normal" if self.around_zero else "one_plus_normal")]
 
     def bind(self, store: WeightStore) -> None:
         self.weight = store.get(self.name)
+        if self.around_zero:
+            self.weight = (self.weight.float() + 1.0).contiguous()
 
     def kernels(self) -> List[str]:
         return ["elementwise"]

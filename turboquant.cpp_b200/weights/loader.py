@@ -39,6 +39,7 @@ class WeightError(ValueError):
 
 @dataclass(frozen=True)
 class WeightSpec:
+    """shape: a dimension of -1 is read from the stored tensor (a table whose length no configuration key gives)."""
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"        # 'normal' | 'one_plus_normal' | 'zeros' | 'ones' | 'int_range'
@@ -113,7 +114,7 @@ def check_plan(index: Dict[str, Tuple[torch.dtype, Tuple[int, ...]]], plan: Sequ
     for n, s in wanted.items():
         if n in index:
             dtype, shape = index[n]
-            if tuple(shape) != tuple(s.shape):
+            if len(shape) != len(s.shape) or any(want not in (-1, got) for want, got in zip(s.shape, shape)):
                 wrong_shape.append((n, tuple(s.shape), tuple(shape)))
             if s.integer == dtype.is_floating_point or dtype == torch.bool:
                 wrong_dtype.append((n, "integer" if s.integer else "floating", str(dtype)))

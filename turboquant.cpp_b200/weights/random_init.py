@@ -103,6 +103,9 @@ class RandomSource(WeightSource):
         spec = self.plan[name]
         device = torch.device(device)
         shape = tuple(spec.shape)
+        if any(d < 0 for d in shape):
+            raise ValueError(f"tensor '{name}' has a size that only a stored tensor gives; random weights need it "
+                             f"in the configuration")
         n = 1
         for d in shape:
             n *= int(d)
