@@ -79,9 +79,12 @@ def distance_bucket(n, rows, far):
     return min(rows - 1, half + step)
 
 
-def visible(i, j, size, keep_first):
-    """Whether position i sees position j: the last `size` positions and the first `keep_first`."""
-    return j <= i and (i - j < size or j < keep_first)
+def visible(i, j, mask):
+    """Whether position i sees position j: the last mask.size positions and the first mask.keep_first; every
+    earlier position if there is no mask."""
+    if not mask:
+        return j <= i
+    return j <= i and (i - j < mask["size"] or j < mask.get("keep_first", 0))
 
 
 # ---- mixers -----------------------------------------------------------------------------------------------------
@@ -99,10 +102,9 @@ def biased_attention(h, w, m, v_first=None):
         v = (1.0 - lam) * v + lam * v_first
     rel = w["rel"]
     rows = rel.shape[0]
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
     out = np.zeros((T, H, dv), dtype=F)
     for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, size, keep)]
+        js = [j for j in range(i + 1) if visible(i, j, m.get("mask"))]
         for a in range(H):
             g = a // (H // G)
             s = np.array([q[i, a] @ k[j, g] * m["scale"] + rel[distance_bucket(i - j, rows, m["bias_max"]), a] for j in js])
@@ -136,10 +138,12 @@ def dense_ff(h, w, limit):
     return capped_glu(h @ w["gate"].T, h @ w["up"].T, limit) @ w["down"].T
 
 
-def route(h, w, r):
+def route(h, w, r, forced=None, margins=None):
     """Per token: (chosen experts, their weights).  Scores are a softmax over all experts; the choice looks at
     score + correction, only inside the groups whose best such value is among the `keep` largest; the weights are
-    the chosen experts' plain scores over their sum."""
+    the chosen experts' plain scores over their sum.  forced [T, top]: these experts instead of the choice (their
+    weights are still this model's); margins: receives per token the smallest gap that decided a choice (between
+    the last kept and the first dropped group, and between the last chosen and the first dropped expert)."""
     z = h @ w["router"].T
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z)
@@ -150,15 +154,26 @@ def route(h, w, r):
         c = s[t] + w["correction"]
         allowed = np.ones(E, dtype=bool)
         groups = r.get("groups")
+        gap = np.inf
         if groups:
             n, per = groups["count"], E // groups["count"]
             best = np.array([c[g * per:(g + 1) * per].max() for g in range(n)])
-            kept = np.argsort(-best, kind="stable")[:groups["keep"]]
+            order = np.argsort(-best, kind="stable")
+            kept = order[:groups["keep"]]
+            if groups["keep"] < n:
+                gap = best[order[groups["keep"] - 1]] - best[order[groups["keep"]]]
             allowed[:] = False
             for g in kept:
                 allowed[g * per:(g + 1) * per] = True
         c = np.where(allowed, c, -np.inf)
-        ids = np.argsort(-c, kind="stable")[:top]
+        order = np.argsort(-c, kind="stable")
+        ids = order[:top]
+        if top < E and np.isfinite(c[order[top]]):
+            gap = min(gap, c[order[top - 1]] - c[order[top]])
+        if margins is not None:
+            margins.append(gap)
+        if forced is not None:
+            ids = np.asarray(forced[t])
         chosen.append(ids)
         weights.append(s[t, ids] / (s[t, ids].sum() + WEIGHT_FLOOR))
     return np.array(chosen), np.array(weights)
@@ -169,10 +184,10 @@ def expert_ff(h, tensors, prefix, limit):
     return dense_ff(h, w, limit)
 
 
-def moe_ff(h, tensors, prefix, mlp):
+def moe_ff(h, tensors, prefix, mlp, forced=None, margins=None):
     r = mlp["router"]
     w = {"router": tensors[prefix + "router"], "correction": tensors[prefix + "correction"]}
-    ids, wts = route(h, w, r)
+    ids, wts = route(h, w, r, forced, margins)
     y = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t], wts[t]):
@@ -195,12 +210,14 @@ class PlainLumevik:
         p = f"l{i}.mix."
         return {n[len(p):]: a for n, a in self.t.items() if n.startswith(p)}
 
-    def forward(self, tokens, streams=None, routing=None):
+    def forward(self, tokens, streams=None, routing=None, forced=None):
         """Logits [T, vocab] of one sequence; `streams` collects the residual stream after every layer, `routing`
-        the experts chosen in every routed layer."""
+        (experts, weights, margins) of every routed layer, in layer order; forced: per routed layer, in that order,
+        the experts [T, top] to take instead of the model's own choice."""
         t, cfg, eps = self.t, self.cfg, self.eps
         x = t["embed"][np.asarray(tokens)].astype(F)
         v_first = None
+        n_routed = 0
         for i, layer in enumerate(cfg["layers"]):
             p, m = f"l{i}.", layer["mixer"]
             h = norm_around_zero(x, t[p + "norm1"], eps)
@@ -219,9 +236,11 @@ class PlainLumevik:
                 if mlp["kind"] == "dense":
                     y = dense_ff(h, {n: t[p + "mlp." + n] for n in ("gate", "up", "down")}, mlp["limit"])
                 else:
-                    y, ids, wts = moe_ff(h, t, p + "mlp.", mlp)
+                    margins = []
+                    y, ids, wts = moe_ff(h, t, p + "mlp.", mlp, None if forced is None else forced[n_routed], margins)
+                    n_routed += 1
                     if routing is not None:
-                        routing.append((ids, wts))
+                        routing.append((ids, wts, np.array(margins)))
                 x = x + y
             if streams is not None:
                 streams.append(x.copy())

@@ -140,7 +140,7 @@ def _attention(m: KeyReader) -> BiasAttentionConfig:
         heads=heads, kv_heads=m.integer("kv_heads", default=heads, minimum=1), dim=m.integer("dim", minimum=1),
         vdim=m.integer("vdim", minimum=1), scale=m.real("scale"), bias_max=m.integer("bias_max", minimum=2),
         bias_rows=m.integer("bias_rows", default=0, minimum=0),
-        window=mask.integer("size", default=0, minimum=0) if mask is not None else 0,
+        window=mask.integer("size", minimum=1) if mask is not None else 0,
         keep_first=mask.integer("keep_first", default=0, minimum=0) if mask is not None else 0,
         v_mix=m.boolean("v_mix", default=False))
     if cfg.heads % cfg.kv_heads:

@@ -231,3 +231,242 @@ TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype,
     }
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Runs of new tokens (prompts), bfloat16, on tensor cores (mma.sync m16n8k16, fp32 accumulation).  A block of four
+// warps takes 64 consecutive queries of one (sequence, head), a warp 16 of them; the keys come a page at a time (64
+// positions: one contiguous piece of the cache, key and value side by side) through a two-stage cp.async ring in
+// shared memory.  Only pages that some query of the block can see are walked: the kept first pages, then the pages
+// of the window; the mask inside a page is exact.  S = Q K^T lives in accumulator fragments, where the bias is
+// added, the mask applied and the online softmax kept per row (fp32); the weights, rounded to bfloat16, are the
+// left operand of the second product with the values read transposed from the same rows.  The sink joins the
+// denominator at the end.  DK, DV: key and value size (multiples of 16 up to 128); the page size is 64.
+// ---------------------------------------------------------------------------------------
+#define BR_Q 64
+#define BR_K 64
+#define BR_WARPS 4
+
+__device__ __forceinline__ void br_ldsm4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void br_ldsm4_t(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void br_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void br_copy16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t br_pack(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(BR_WARPS * 32)
+bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                           const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
+                           const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
+                           const int* __restrict__ page_table, int table_stride, int window, int keep_first,
+                           float scale, __nv_bfloat16* __restrict__ out, int nh, int nkv, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int DR = DK + DV, LD = DR + 8;                 // a shared-memory row: key, value, 16 bytes of padding
+    extern __shared__ __align__(16) uint8_t br_smem[];
+    __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(br_smem);      // [2][BR_K][LD]
+    const int seq = blockIdx.y, h = blockIdx.z;
+    const int t0 = cu_seqlens[seq], n_run = cu_seqlens[seq + 1] - t0;
+    const int a0 = blockIdx.x * BR_Q;                        // first query of the block within the run
+    if (a0 >= n_run) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = h / (nh / nkv);
+    const int pos0 = seq_start[seq] + a0;                    // position of the block's first query
+    const int n_q = min(BR_Q, n_run - a0);
+    const int pos_last = pos0 + n_q - 1;
+    const int* table = page_table + (size_t)seq * table_stride;
+    // pages to walk: [0, kept) and [first, last]
+    const int first = window > 0 ? max(0, pos0 + 1 - window) / BR_K : 0;
+    const int last = pos_last / BR_K;
+    const int kept = window > 0 ? min((keep_first + BR_K - 1) / BR_K, first) : 0;
+    const int n_tiles = kept + (last - first + 1);
+
+    auto load_tile = [&](int i, int stage) {
+        const int pg = i < kept ? i : first + (i - kept);
+        const int page = TQ_CHECKED(table[TQ_CHECKED(pg, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+        const __nv_bfloat16* src = cache + ((size_t)max(page, 0) * nkv + g) * BR_K * DR;
+        __nv_bfloat16* dst = tiles + (size_t)stage * BR_K * LD;
+        constexpr int CPR = DR / 8;                          // 16-byte pieces of a row
+        for (int c = threadIdx.x; c < BR_K * CPR; c += BR_WARPS * 32) {
+            const int r = c / CPR, k = c % CPR;
+            br_copy16(dst + r * LD + k * 8, src + r * DR + k * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(0, 0);
+
+    // this warp's 16 queries as left-operand fragments
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;           // the thread's two rows within the block
+    uint32_t qf[DK / 16][4];
+    {
+        const __nv_bfloat16* q_lo = q + ((size_t)(t0 + a0 + r_lo) * nh + h) * DK + (lane & 3) * 2;
+        const __nv_bfloat16* q_hi = q + ((size_t)(t0 + a0 + r_hi) * nh + h) * DK + (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            qf[ks][0] = r_lo < n_q ? *reinterpret_cast<const uint32_t*>(q_lo + ks * 16) : 0u;
+            qf[ks][1] = r_hi < n_q ? *reinterpret_cast<const uint32_t*>(q_hi + ks * 16) : 0u;
+            qf[ks][2] = r_lo < n_q ? *reinterpret_cast<const uint32_t*>(q_lo + ks * 16 + 8) : 0u;
+            qf[ks][3] = r_hi < n_q ? *reinterpret_cast<const uint32_t*>(q_hi + ks * 16 + 8) : 0u;
+        }
+    }
+    const float* bias_h = bias_t ? bias_t + (size_t)h * (far + 1) : nullptr;
+    const float sink_h = sink ? sink[h] : -INFINITY;
+    float m_lo = sink_h, m_hi = sink_h, l_lo = 0.f, l_hi = 0.f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    const int i_lo = pos0 + r_lo, i_hi = pos0 + r_hi;                    // the two rows' positions
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it & 1;
+        if (it + 1 < n_tiles) {
+            load_tile(it + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __nv_bfloat16* tile = tiles + (size_t)stage * BR_K * LD;
+        const int p_base = (it < kept ? it : first + (it - kept)) * BR_K;     // position of the tile's first key
+        // a warp whose rows see nothing of this tile skips it (the tile lies wholly behind its last query)
+        const bool any = p_base <= pos0 + min(warp * 16 + 15, n_q - 1);
+        if (any) {
+            float s[BR_K / 8][4];
+#pragma unroll
+            for (int n = 0; n < BR_K / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < DK / 16; ++ks) {
+#pragma unroll
+                for (int n = 0; n < BR_K / 8; n += 2) {
+                    uint32_t b[4];
+                    const int mi = lane >> 3;
+                    br_ldsm4(b, tile + ((n + (mi >> 1)) * 8 + (lane & 7)) * LD + ks * 16 + (mi & 1) * 8);
+                    br_mma(s[n], qf[ks], b[0], b[1]);
+                    br_mma(s[n + 1], qf[ks], b[2], b[3]);
+                }
+            }
+            // scale, bias, mask; the rows' maxima
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < BR_K / 8; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int p = p_base + n * 8 + (lane & 3) * 2 + (c & 1);
+                    const int i = (c & 2) ? i_hi : i_lo;
+                    const int d = i - p;
+                    const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
+                    float v = s[n][c] * scale;
+                    if (bias_h && see) v += __ldg(bias_h + min(d, far));
+                    v = see ? v : -INFINITY;
+                    s[n][c] = v;
+                    if (c & 2) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+                }
+            }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float u_lo = mn_lo == -INFINITY ? 0.f : mn_lo, u_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+            const float c_lo = expf(m_lo - u_lo), c_hi = expf(m_hi - u_hi);      // exp(-inf) = 0 before the first key
+            m_lo = mn_lo; m_hi = mn_hi;
+            l_lo *= c_lo; l_hi *= c_hi;
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) { o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi; }
+#pragma unroll
+            for (int n = 0; n < BR_K / 8; ++n) {
+                s[n][0] = expf(s[n][0] - u_lo); s[n][1] = expf(s[n][1] - u_lo);
+                s[n][2] = expf(s[n][2] - u_hi); s[n][3] = expf(s[n][3] - u_hi);
+                l_lo += s[n][0] + s[n][1];
+                l_hi += s[n][2] + s[n][3];
+            }
+            // O += P V: sixteen keys at a time
+#pragma unroll
+            for (int kk = 0; kk < BR_K / 16; ++kk) {
+                uint32_t a[4];
+                a[0] = br_pack(s[2 * kk][0], s[2 * kk][1]);
+                a[1] = br_pack(s[2 * kk][2], s[2 * kk][3]);
+                a[2] = br_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                a[3] = br_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n = 0; n < DV / 8; n += 2) {
+                    uint32_t b[4];
+                    const int mi = lane >> 3;
+                    br_ldsm4_t(b, tile + (kk * 16 + (mi & 1) * 8 + (lane & 7)) * LD + DK + (n + (mi >> 1)) * 8);
+                    br_mma(o[n], a, b[0], b[1]);
+                    br_mma(o[n + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();               // the stage is loaded again two tiles on
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (sink) { l_lo += expf(sink_h - m_lo); l_hi += expf(sink_h - m_hi); }
+    const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+    __nv_bfloat16* o_lo = out + ((size_t)(t0 + a0 + r_lo) * nh + h) * DV + (lane & 3) * 2;
+    __nv_bfloat16* o_hi = out + ((size_t)(t0 + a0 + r_hi) * nh + h) * DV + (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+        if (r_lo < n_q) *reinterpret_cast<uint32_t*>(o_lo + n * 8) = br_pack(o[n][0] * inv_lo, o[n][1] * inv_lo);
+        if (r_hi < n_q) *reinterpret_cast<uint32_t*>(o_hi + n * 8) = br_pack(o[n][2] * inv_hi, o[n][3] * inv_hi);
+    }
+}
+
+template <int DK, int DV>
+int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
+                     const int* cu_seqlens, const int* seq_start, const int* page_table, int table_stride, int window,
+                     int keep_first, float scale, void* out, int n_seqs, int max_run, int nh, int nkv, int n_pages,
+                     cudaStream_t stream) {
+    auto kern = bias_attention_runs_kernel<DK, DV>;
+    const int smem = 2 * BR_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) TQ_FAIL(-1, "bias_attention_runs: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((max_run + BR_Q - 1) / BR_Q, n_seqs, nh);
+    tq_launch(grid, BR_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far,
+        sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, scale, (__nv_bfloat16*)out, nh, nkv, n_pages);
+    return 0;
+}
+
+// bias_t: the bias per head and distance, [heads][far + 1] (the transpose of what tq_bias_attention takes).
+TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_dtype, const float* bias_t, int far,
+                                     const float* sink, const int* cu_seqlens, const int* seq_start,
+                                     const int* page_table, int table_stride, int page_size, int window,
+                                     int keep_first, float scale, void* out, int n_seqs, int max_run, int nh, int nkv,
+                                     int dk, int dv, int n_pages, cudaStream_t stream) {
+    if (n_seqs == 0 || max_run == 0) return 0;
+    TQ_REQUIRE(act_dtype == TQ_BF16, "bias_attention_runs: bfloat16 only");
+    TQ_REQUIRE(page_size == BR_K, "bias_attention_runs: pages of %d positions, not %d", BR_K, page_size);
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "bias_attention_runs: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    TQ_REQUIRE(nh <= 65535 && n_seqs <= 65535, "bias_attention_runs: %d heads or %d sequences exceed the grid limit", nh, n_seqs);
+    TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_runs: negative window, kept positions or distance");
+    int rc = -2;
+#define BR_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_runs<DK_, DV_>(q, cache, bias_t, far, sink, cu_seqlens, \
+        seq_start, page_table, table_stride, window, keep_first, scale, out, n_seqs, max_run, nh, nkv, n_pages, stream);
+    BR_CASE(32, 32) BR_CASE(32, 64) BR_CASE(32, 128) BR_CASE(64, 32) BR_CASE(64, 64) BR_CASE(64, 128)
+    BR_CASE(128, 32) BR_CASE(128, 64) BR_CASE(128, 128)
+#undef BR_CASE
+    TQ_REQUIRE(rc != -2, "bias_attention_runs: key size %d and value size %d must each be 32, 64 or 128", dk, dv);
+    if (rc) return rc;
+    TQ_CHECK_LAUNCH("bias_attention_runs");
+    return 0;
+}

@@ -41,9 +41,39 @@ def kv_write(qkv: torch.Tensor, q_out: torch.Tensor, cache: Optional[torch.Tenso
         c_int(cache.shape[0] if cache is not None else 0), stream()))
 
 
-def runs_usable(dk: int, dv: int, page_size: int) -> bool:
-    """Whether the kernel for runs of new tokens takes these sizes."""
-    return False
+RUN_SIZES = (32, 64, 128)      # key and value sizes the tensor-core kernel for runs is built for
+
+
+def runs_usable(dtype: torch.dtype, dk: int, dv: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel for runs of new tokens takes this shape: bfloat16, key and value sizes of 32,
+    64 or 128, pages of 64 positions (TQ_BIAS_NO_MMA=1 switches it off)."""
+    import os
+    return (dtype == torch.bfloat16 and dk in RUN_SIZES and dv in RUN_SIZES and page_size == 64
+            and os.environ.get("TQ_BIAS_NO_MMA", "") in ("", "0"))
+
+
+def attention_runs(q: torch.Tensor, cache: torch.Tensor, bias_t: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                   cu_seqlens: torch.Tensor, seq_start: torch.Tensor, page_table: torch.Tensor, page_size: int,
+                   window: int, keep_first: int, scale: float, out: torch.Tensor, n_seqs: int, max_run: int,
+                   heads: int, kv_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The same attention for steps with runs of new tokens (prompts), bfloat16 on tensor cores: blocks of 64
+    queries of a (sequence, head) walk the pages they can see.  bias_t float32 [heads, far + 1]: the bias per head
+    and distance (the transpose of what `attention` takes)."""
+    far = 0
+    if bias_t is not None:
+        want_f32(bias_t, "the distance bias")
+        if bias_t.dim() != 2 or bias_t.shape[0] != heads:
+            raise KernelError("attention_runs: the distance bias must be [heads, distances]")
+        far = bias_t.shape[1] - 1
+    if sink is not None:
+        want_f32(sink, "the sink")
+    lib = load_kernel(_LIB)
+    check(_LIB, lib.tq_bias_attention_runs(
+        ptr(q), ptr(cache), c_int(code(q.dtype)), ptr(bias_t), c_int(far), ptr(sink), ptr(cu_seqlens), ptr(seq_start),
+        ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale),
+        ptr(out), c_int(n_seqs), c_int(max_run), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+        c_int(cache.shape[0]), stream()))
+    return out
 
 
 def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:

@@ -66,7 +66,7 @@ class BiasedWindowAttentionMixer(Mixer):
         self.bias_rows, self.bias_far, self.has_sink = int(bias_rows), int(bias_far), bool(sink)
         self.mix_values, self.mix_first = mix_values, bool(mix_first)
         self.q_size, self.k_size, self.v_size = heads * dim, kv_heads * dim, kv_heads * vdim
-        self.w_qkv = self.w_o = self.bias = self.sink = None
+        self.w_qkv = self.w_o = self.bias = self.bias_t = self.sink = None
         self.mix = 0.0
 
     @staticmethod
@@ -97,6 +97,7 @@ class BiasedWindowAttentionMixer(Mixer):
             self.bias_rows = rel.shape[0]
             index = torch.tensor(distance_buckets(rel.shape[0], self.bias_far), dtype=torch.long, device=rel.device)
             self.bias = rel[index].contiguous()                                  # [far + 1, heads], a row per distance
+            self.bias_t = self.bias.t().contiguous()                             # [heads, far + 1] for the kernel for runs
         if self.has_sink:
             self.sink = torch.zeros(self.heads, dtype=torch.float32, device=store.device)
         if self.mix_values is not None:
@@ -132,8 +133,8 @@ class BiasedWindowAttentionMixer(Mixer):
         KB.kv_write(qkv, q, cache.kv if cache.writes else None, keep, other, self.mix, ctx.positions, ctx.seq_of_token,
                     cache.page_table, cache.page_size, self.heads, self.kv_heads, self.dim, self.vdim)
         o = torch.empty((T, self.heads * self.vdim), dtype=act, device=dev)
-        if ctx.max_q_len >= self.RUNS_MIN and KB.runs_usable(self.dim, self.vdim, cache.page_size):
-            KB.attention_runs(q, cache.kv, self.bias, self.sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table,
+        if ctx.max_q_len >= self.RUNS_MIN and KB.runs_usable(act, self.dim, self.vdim, cache.page_size):
+            KB.attention_runs(q, cache.kv, self.bias_t, self.sink, ctx.cu_seqlens, ctx.seq_start, cache.page_table,
                               cache.page_size, self.window, self.keep_first, self.scale, o, ctx.n_seqs, ctx.max_q_len,
                               self.heads, self.kv_heads, self.dim, self.vdim)
         else:
