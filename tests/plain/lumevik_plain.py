@@ -88,29 +88,40 @@ def visible(i, j, mask):
 
 
 # ---- mixers -----------------------------------------------------------------------------------------------------
+def biased_attention_core(q, k, v, rel, m):
+    """q [T, H, d], k [T, G, d], v [T, G, dv] of one sequence; rel [rows, H] or None.  Per query and head: scores with
+    the distance bias over the visible positions, a softmax whose denominator counts one more (a key of score 0
+    without a value), the weighted sum of the values."""
+    T, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    out = np.zeros((T, H, dv), dtype=F)
+    for i in range(T):
+        js = [j for j in range(i + 1) if visible(i, j, m.get("mask"))]
+        for a in range(H):
+            g = a // (H // G)
+            s = np.array([q[i, a] @ k[j, g] * m["scale"]
+                          + (rel[distance_bucket(i - j, rel.shape[0], m["bias_max"]), a] if rel is not None else 0.0) for j in js])
+            e = np.exp(s)
+            p = e / (1.0 + e.sum())
+            out[i, a] = sum(p[n] * v[j, g] for n, j in enumerate(js))
+    return out
+
+
+def mix_values(v, v_first, lam):
+    return (1.0 - lam) * v + lam * v_first
+
+
 def biased_attention(h, w, m, v_first=None):
-    """Grouped-query attention with a table of distance biases, a window that keeps the first positions, a softmax
-    whose denominator counts one more (a key of score 0 without a value), and values mixed with those of the first
-    such layer.  Returns (output, the values as they would be cached)."""
+    """Grouped-query attention without rotation: projections, values mixed with those of the first such layer,
+    the core above, the output projection.  Returns (output, the values as they would be cached)."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w["q"].T).reshape(T, H, d)
     k = (h @ w["k"].T).reshape(T, G, d)
     v = (h @ w["v"].T).reshape(T, G, dv)
     if m.get("v_mix") and v_first is not None:
-        lam = float(w["vmix"])
-        v = (1.0 - lam) * v + lam * v_first
-    rel = w["rel"]
-    rows = rel.shape[0]
-    out = np.zeros((T, H, dv), dtype=F)
-    for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, m.get("mask"))]
-        for a in range(H):
-            g = a // (H // G)
-            s = np.array([q[i, a] @ k[j, g] * m["scale"] + rel[distance_bucket(i - j, rows, m["bias_max"]), a] for j in js])
-            e = np.exp(s)
-            p = e / (1.0 + e.sum())
-            out[i, a] = sum(p[n] * v[j, g] for n, j in enumerate(js))
+        v = mix_values(v, v_first, float(w["vmix"]))
+    out = biased_attention_core(q, k, v, w["rel"], m)
     return out.reshape(T, H * dv) @ w["o"].T, v
 
 
