@@ -84,7 +84,7 @@ def test_selection_with_corrected_scores_and_groups(E, k, groups, keep, correcte
     rng = np.random.default_rng(E * 31 + k)
     T, H = 97, 24
     h = rng.standard_normal((T, H))
-    w = {"router": 1.5 * rng.standard_normal((E, H)), "correction": (0.3 / E * rng.standard_normal(E)) if corrected else np.zeros(E)}
+    w = {"router": 0.3 * rng.standard_normal((E, H)), "correction": (0.3 / E * rng.standard_normal(E)) if corrected else np.zeros(E)}
     sg = rng.standard_normal((1, H))
     r = {"experts": E, "top": k, "groups": {"count": groups, "keep": keep}}
     margins = []
@@ -99,7 +99,7 @@ def test_selection_with_corrected_scores_and_groups(E, k, groups, keep, correcte
     assert rel(scale, P.sigmoid(h @ sg.T)[:, 0]) < 1e-5
     gi, gw = got_ids.cpu().numpy(), got_w.cpu().numpy()
     clear = np.array(margins) > 1e-6
-    assert clear.mean() > 0.9
+    assert clear.mean() > 0.8
     for t in np.nonzero(clear)[0]:
         assert sorted(gi[t].tolist()) == sorted(ids[t].tolist()), (t, gi[t], ids[t])
         order_g, order_p = np.argsort(gi[t]), np.argsort(ids[t])
