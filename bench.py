@@ -150,8 +150,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--kernel-table", default="", help="write a per-kernel time table of a few decode steps and of a "
                     "prefill to this file (torch profiler; not part of any timed number)")
-    ap.add_argument("--design", choices=["nuforax"], default="", help="instead of the default workload: prompt and decode "
-                    "speed of this design at layer sizes of a real model (random weights), beside the dense Qwen2 decoder of "
+    ap.add_argument("--design", choices=["nuforax", "lumevik"], default="", help="instead of the default workload: prompt and decode "
+                    "speed of this design at layer sizes of a real model (random weights), beside the closest Qwen2 decoder of "
                     "equal width, depth and heads")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of the sizes to run")
     args = ap.parse_args()
@@ -344,6 +344,36 @@ def dense_qwen2_config(width, layers, heads, window, inter, vocab):
                 max_position_embeddings=8192, tie_word_embeddings=True)
 
 
+def lumevik_config(width, layers, heads, kv_heads, dim, window, keep_first, rank, q_rank, ff, experts, top, e_ff, s_ff, vocab):
+    """Layers in pairs: latent attention with a dense feed-forward, then windowed attention with routed experts."""
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff, "limit": 7.0},
+           "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "q_rank": q_rank, "scale": dim ** -0.5}}
+    att = {"type": "attention",
+           "mlp": {"kind": "moe", "expert": {"ff": e_ff, "limit": 7.0}, "shared": {"ff": s_ff, "limit": 7.0},
+                   "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}},
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "bias_max": 2048,
+                     "bias_rows": 32, "mask": {"size": window, "keep_first": keep_first}, "v_mix": True}}
+    return {"architecture": "Lumevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [lat if i % 2 == 0 else att for i in range(layers)]}
+
+
+def sparse_qwen2_config(width, layers, heads, kv_heads, dim, window, ff, experts, top, e_ff, s_ff, vocab):
+    """The Qwen2 MoE decoder with the same widths: dense feed-forwards on the even layers, experts on the odd ones,
+    a window on every layer."""
+    return dict(A27B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
+                head_dim=dim, num_experts=experts, num_experts_per_tok=top, moe_intermediate_size=e_ff,
+                shared_expert_intermediate_size=s_ff, intermediate_size=ff, vocab_size=vocab, use_sliding_window=True,
+                sliding_window=window, max_window_layers=0, max_position_embeddings=8192, tie_word_embeddings=False,
+                decoder_sparse_step=1, mlp_only_layers=list(range(0, layers, 2)), norm_topk_prob=True)
+
+
+LUMEVIK_SIZES = {
+    # name: (width, layers, heads, kv heads, head size, window, kept first, kv_rank, q_rank, dense ff, experts, top, expert ff,
+    #        shared ff, vocab)
+    "w1024": (1024, 4, 8, 2, 128, 1024, 4, 256, 384, 2816, 32, 4, 704, 2816, 32768),
+    "w2048": (2048, 4, 16, 4, 128, 1024, 4, 512, 768, 5632, 60, 4, 1408, 5632, 32768),
+}
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, dim, rot, vdim, rank, window, ff, ssm heads, ssm vdim, ssm state, ssm groups, vocab)
     "w1024": (1024, 6, 8, 64, 64, 64, 256, 1024, 4096, 32, 64, 64, 1, 32768),
@@ -425,6 +455,8 @@ def design_compare(args) -> int:
             torch.cuda.empty_cache()
         return out
 
+    if args.design == "lumevik":
+        return lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup)
     result = {"metric": "prompt and decode speed, Nuforax beside the dense Qwen2 decoder of equal width", "unit": "tokens/s",
               "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
               "peaks": pk, "sizes": {}}
@@ -459,6 +491,38 @@ def design_compare(args) -> int:
         del model
         gc.collect()
         torch.cuda.empty_cache()
+        result["sizes"][name] = entry
+    result["clocks"] = clocks.stop()
+    print(json.dumps(result))
+    return 0
+
+
+def lumevik_compare(args, tq, measure, weights_bytes, pk, rng, prompt, steps, warmup) -> int:
+    """The Lumevik decoder beside the Qwen2 MoE decoder of the same widths, heads, window, experts and feed-forward
+    sizes (which has attention with rotation on every layer where Lumevik alternates latent and windowed attention)."""
+    import torch
+    result = {"metric": "prompt and decode speed, Lumevik beside the Qwen2 MoE decoder of equal sizes", "unit": "tokens/s",
+              "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic token ids, seeded random weights",
+              "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.sizes.split(","):
+        if name not in LUMEVIK_SIZES:
+            print(json.dumps({"error": f"unknown size '{name}'; known: {sorted(LUMEVIK_SIZES)}"}))
+            return 2
+        (W, L, H, G, D, window, keep, rank, q_rank, ff, E, top, e_ff, s_ff, V) = LUMEVIK_SIZES[name]
+        entry = {}
+        for who, cfg in (("lumevik", lumevik_config(W, L, H, G, D, window, keep, rank, q_rank, ff, E, top, e_ff, s_ff, V)),
+                         ("qwen2_moe", sparse_qwen2_config(W, L, H, G, D, window, ff, E, top, e_ff, s_ff, V))):
+            model = tq.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            entry[who] = dict(measure(model, V), config={"width": W, "layers": L, "heads": H, "kv_heads": G, "head_size": D,
+                                                         "window": window, "dense_ff": ff, "experts": E, "top": top,
+                                                         "expert_ff": e_ff, "shared_ff": s_ff})
+            if args.kernel_table:
+                kernel_table(tq, model, rng, V, 8, args.kernel_table + f".{who}_{name}.txt", prompt=prompt, context=prompt + 128)
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
         result["sizes"][name] = entry
     result["clocks"] = clocks.stop()
     print(json.dumps(result))
