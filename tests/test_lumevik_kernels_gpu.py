@@ -123,6 +123,9 @@ ATT_CASES = [
     (150, 3, 3, 128, 128, 0, 0, 32, 120),         # no window
     (131, 6, 2, 24, 40, 33, 66, 10, 50),          # sizes only the token kernel takes; kept positions beyond a page
     (260, 2, 2, 32, 32, 1, 129, 4, 3),            # a window of one: itself and the kept first positions
+    (190, 16, 2, 64, 64, 50, 3, 12, 60),          # eight heads a key/value head
+    (140, 24, 2, 128, 32, 40, 70, 12, 60),        # twelve: the heads of a key/value head are shared out over blocks
+    (100, 8, 4, 32, 128, 30, 2, 6, 40),           # a value four times the key
 ]
 
 
@@ -159,10 +162,11 @@ def test_cache_write_and_both_attention_kernels(case, dtype):
     sink = torch.zeros(H, dtype=torch.float32, device=DEV)
     tol = 2e-5 if dtype == torch.float32 else 1.5e-2
     for n_splits in (1, 2, 5, 64):
-        out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
-        KB.attention(q_dev, cache, bias, sink, positions, seq_of_token, table, 64, window, keep, m["scale"], out, H, G,
-                     dk, dv, n_splits=n_splits)
-        assert rel(out, want) < tol, n_splits
+        for bias_t in (None, bias.t().contiguous()):          # a block per head; a block per key/value head where built
+            out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
+            KB.attention(q_dev, cache, bias, sink, positions, seq_of_token, table, 64, window, keep, m["scale"], out, H, G,
+                         dk, dv, n_splits=n_splits, bias_t=bias_t)
+            assert rel(out, want) < tol, (n_splits, bias_t is not None)
     if KB.runs_usable(dtype, dk, dv, 64):
         # the same tokens as one run, and as a run that continues a sequence (its first 77 tokens already cached)
         for start in (0, 77):

@@ -233,6 +233,246 @@ TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype,
 }
 
 // ---------------------------------------------------------------------------------------
+// Token form for grouped queries, bfloat16, key and value sizes of 32, 64 or 128: grid (token x head chunks, kv head,
+// range), 4 warps.  A block keeps up to GC query heads of one key/value head in registers and reads every cached row
+// once for all of them: a row's key is read by LPK = DK / 8 lanes with one 16-byte load each, so a warp covers
+// 32 / LPK rows per instruction and eight rows per iteration, the next iteration's loads in flight during this
+// one's arithmetic; the value's 16-byte pieces are shared out over the same lanes.  Online softmax per head and
+// lane group (fp32), merged over the lane groups by shuffles and over the warps through shared memory, in a fixed
+// order.  The ranges' states go to `partial` as in the form above and are joined by the same merge.
+// bias_t: [heads][far + 1].
+// ---------------------------------------------------------------------------------------
+struct BaRaw { uint4 v; };
+__device__ __forceinline__ BaRaw ba_fetch(const __nv_bfloat16* p) { BaRaw r; r.v = *reinterpret_cast<const uint4*>(p); return r; }
+__device__ __forceinline__ void ba_widen(const BaRaw& r, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+
+template <int DK, int DV, int GC>
+__global__ void __launch_bounds__(BA_WARPS * 32)
+bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                            const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ page_table, int table_stride, int page_size, int window,
+                            int keep_first, float scale, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int LPK = DK / 8, KPI = 32 / LPK, LOADS = KPI >= 8 ? 1 : 8 / KPI, GS = KPI * LOADS;
+    constexpr int NV8 = DV / 8, NVC = NV8 > LPK ? NV8 / LPK : 1, DR = DK + DV;
+    __shared__ float s_m[BA_WARPS][GC], s_l[BA_WARPS][GC];
+    __shared__ float s_acc[BA_WARPS][GC][DV];
+    const int G_all = nh / nkv;
+    const int chunks = (G_all + GC - 1) / GC;
+    const int t = blockIdx.x / chunks, chunk = blockIdx.x - t * chunks, g = blockIdx.y, split = blockIdx.z;
+    const int h0 = g * G_all + chunk * GC;                   // the block's first head
+    const int G = min(GC, G_all - chunk * GC);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LPK, part = lane / LPK;           // part: which of the KPI rows of a load
+    const int pos = positions[t];
+    const BaSpan span = ba_span(pos, window, keep_first);
+    int per = (span.count + n_splits - 1) / n_splits;
+    per = (per + GS - 1) / GS * GS;
+    const int n0 = split * per, n1 = min(span.count, n0 + per);
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+
+    BaRaw kr[LOADS], vr[LOADS][NVC];
+    auto fetch_group = [&](int base) {
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) {
+            const int n = min(base + j * KPI + part, n1 - 1);            // rows past the range repeat its last row (masked below)
+            const int p = span.at(n);
+            const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+            const __nv_bfloat16* row = cache + (((size_t)page * nkv + g) * page_size + p % page_size) * DR;
+            kr[j] = ba_fetch(row + sub * 8);
+#pragma unroll
+            for (int c = 0; c < NVC; ++c)
+                if (sub + c * LPK < NV8) vr[j][c] = ba_fetch(row + DK + (sub + c * LPK) * 8);
+        }
+    };
+    if (n0 + warp * GS < n1) fetch_group(n0 + warp * GS);
+
+    float qv[GC][8], acc[GC][NVC][8], m[GC], l[GC];
+#pragma unroll
+    for (int h = 0; h < GC; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+        if (sink != nullptr && split == 0 && warp == 0 && part == 0 && h < G) { m[h] = sink[h0 + h]; l[h] = 1.f; }
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (h < G) { const BaRaw r = ba_fetch(q + ((size_t)t * nh + h0 + h) * DK + sub * 8); ba_widen(r, f); }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qv[h][i] = f[i] * scale;
+#pragma unroll
+        for (int c = 0; c < NVC; ++c)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[h][c][i] = 0.f;
+    }
+    for (int base = n0 + warp * GS; base < n1; base += BA_WARPS * GS) {
+        float kf[LOADS][8], vf[LOADS][NVC][8];
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) {
+            ba_widen(kr[j], kf[j]);
+#pragma unroll
+            for (int c = 0; c < NVC; ++c) {
+                if (sub + c * LPK < NV8) ba_widen(vr[j][c], vf[j][c]);
+                else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) vf[j][c][i] = 0.f;
+                }
+            }
+        }
+        if (base + BA_WARPS * GS < n1) fetch_group(base + BA_WARPS * GS);      // the next rows fly during this group's math
+        float s[LOADS][GC];
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j)
+#pragma unroll
+            for (int h = 0; h < GC; ++h) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d = fmaf(qv[h][i], kf[j][i], d);
+                s[j][h] = d;
+            }
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j)
+#pragma unroll
+                for (int h = 0; h < GC; ++h) s[j][h] += __shfl_xor_sync(0xffffffffu, s[j][h], o);
+#pragma unroll
+        for (int h = 0; h < GC; ++h) {
+            if (h >= G) continue;
+            float mx = m[h];
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) {
+                const int n = base + j * KPI + part;
+                if (n < n1) {
+                    if (bias_t) s[j][h] += __ldg(bias_t + (size_t)(h0 + h) * (far + 1) + min(pos - span.at(n), far));
+                } else s[j][h] = -INFINITY;
+                mx = fmaxf(mx, s[j][h]);
+            }
+            if (mx == -INFINITY) continue;                 // nothing visible yet for this lane group
+            const float corr = expf(m[h] - mx);
+            float lsum = l[h] * corr;
+#pragma unroll
+            for (int c = 0; c < NVC; ++c)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[h][c][i] *= corr;
+#pragma unroll
+            for (int j = 0; j < LOADS; ++j) {
+                const float pe = expf(s[j][h] - mx);       // exp(-inf) = 0 for masked rows
+                lsum += pe;
+#pragma unroll
+                for (int c = 0; c < NVC; ++c)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[h][c][i] = fmaf(pe, vf[j][c][i], acc[h][c][i]);
+            }
+            m[h] = mx; l[h] = lsum;
+        }
+    }
+    // the warp's KPI lane groups, joined by shuffles (the same order for every launch)
+#pragma unroll
+    for (int h = 0; h < GC; ++h) {
+#pragma unroll
+        for (int o = LPK; o < 32; o <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+            const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+            const float M = fmaxf(m[h], mo);
+            const float fa = m[h] == -INFINITY ? 0.f : expf(m[h] - M), fb = mo == -INFINITY ? 0.f : expf(mo - M);
+            l[h] = l[h] * fa + lo * fb;
+#pragma unroll
+            for (int c = 0; c < NVC; ++c)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float ao = __shfl_xor_sync(0xffffffffu, acc[h][c][i], o);
+                    acc[h][c][i] = acc[h][c][i] * fa + ao * fb;
+                }
+            m[h] = M;
+        }
+        if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+        if (part == 0) {
+#pragma unroll
+            for (int c = 0; c < NVC; ++c)
+                if (sub + c * LPK < NV8) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) s_acc[warp][h][(sub + c * LPK) * 8 + i] = acc[h][c][i];
+                }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * DV; idx += blockDim.x) {
+        const int h = idx / DV, d = idx % DV;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < BA_WARPS; ++w) M = fmaxf(M, s_m[w][h]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < BA_WARPS; ++w) {
+            const float f = s_m[w][h] == -INFINITY ? 0.f : expf(s_m[w][h] - M);
+            L += s_l[w][h] * f;
+            a += s_acc[w][h][d] * f;
+        }
+        if (n_splits == 1) {
+            out[((size_t)t * nh + h0 + h) * DV + d] = __float2bfloat16_rn(a / L);
+            continue;
+        }
+        float* dst = partial + (((size_t)t * nh + h0 + h) * n_splits + split) * (DV + 2);
+        dst[2 + d] = a;
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+    }
+}
+
+// Heads a block of the grouped form keeps for `per_kv` query heads per key/value head and this shape (0: the shape
+// is not built).
+static int ba_group_heads(int dk, int dv, int per_kv) {
+    if (!((dk == 32 || dk == 64 || dk == 128) && (dv == 32 || dv == 64 || dv == 128))) return 0;
+    const int nvc = dv / 8 > dk / 8 ? dv / dk : 1;
+    int gc = per_kv >= 8 ? 8 : (per_kv > 2 ? 4 : per_kv);
+    if (dk == 128 && gc > 4) gc = 4;          // four loads of a lane in flight: eight heads would spill registers
+    while (gc * nvc > 8 && gc > 1) gc >>= 1;
+    return gc;
+}
+TQ_EXPORT int tq_bias_attention_group_heads(int dk, int dv, int per_kv) { return ba_group_heads(dk, dv, per_kv); }
+
+TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
+                                      const int* positions, const int* seq_of_token, const int* page_table,
+                                      int table_stride, int page_size, int window, int keep_first, float scale, void* out,
+                                      float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
+                                      int n_pages, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "bias_attention_group: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    const int gc = ba_group_heads(dk, dv, nh / nkv);
+    TQ_REQUIRE(gc > 0, "bias_attention_group: key size %d and value size %d must each be 32, 64 or 128", dk, dv);
+    TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_group: negative window, kept positions or distance");
+    TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && nkv <= 65535, "bias_attention_group: %d ranges or %d key/value heads exceed the grid limit", n_splits, nkv);
+    TQ_REQUIRE(n_splits == 1 || partial != nullptr, "bias_attention_group: %d ranges need scratch for their states", n_splits);
+    const int chunks = (nh / nkv + gc - 1) / gc;
+    dim3 grid(T_ * chunks, nkv, n_splits);
+    bool done = false;
+#define BG_CASE(DK_, DV_, GC_)                                                                                        \
+    if (!done && dk == DK_ && dv == DV_ && gc == GC_) {                                                               \
+        tq_launch(grid, BA_WARPS * 32, 0, stream)(bias_attention_group_kernel<DK_, DV_, GC_>, (const __nv_bfloat16*)q,  \
+            (const __nv_bfloat16*)cache, bias_t, far, sink, positions, seq_of_token, page_table, table_stride, page_size, \
+            window, keep_first, scale, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
+        done = true;                                                                                                  \
+    }
+#define BG_SHAPE(DK_, DV_) BG_CASE(DK_, DV_, 1) BG_CASE(DK_, DV_, 2) BG_CASE(DK_, DV_, 4)
+    BG_SHAPE(32, 32) BG_SHAPE(64, 32) BG_SHAPE(64, 64) BG_SHAPE(128, 32) BG_SHAPE(128, 64) BG_SHAPE(128, 128)
+    BG_CASE(32, 32, 8) BG_CASE(64, 32, 8) BG_CASE(64, 64, 8)
+    BG_CASE(32, 64, 1) BG_CASE(32, 64, 2) BG_CASE(32, 64, 4) BG_CASE(64, 128, 1) BG_CASE(64, 128, 2) BG_CASE(64, 128, 4)
+    BG_CASE(32, 128, 1) BG_CASE(32, 128, 2)
+#undef BG_SHAPE
+#undef BG_CASE
+    TQ_REQUIRE(done, "bias_attention_group: no kernel for sizes %d, %d with %d heads a block", dk, dv, gc);
+    TQ_CHECK_LAUNCH("bias_attention_group");
+    if (n_splits > 1) {
+        tq_launch(T_ * nh, dv >= 128 ? 128 : 64, 0, stream)(bias_attention_merge_kernel<__nv_bfloat16>, partial, n_splits, dv, (__nv_bfloat16*)out);
+        TQ_CHECK_LAUNCH("bias_attention_merge");
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
 // Runs of new tokens (prompts), bfloat16, on tensor cores (mma.sync m16n8k16, fp32 accumulation).  A block of four
 // warps takes 64 consecutive queries of one (sequence, head), a warp 16 of them; the keys come a page at a time (64
 // positions: one contiguous piece of the cache, key and value side by side) through a two-stage cp.async ring in
@@ -267,7 +507,7 @@ __device__ __forceinline__ uint32_t br_pack(float a, float b) {
 }
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(BR_WARPS * 32)
+__global__ void __launch_bounds__(BR_WARPS * 32, 3)
 bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                            const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
@@ -278,6 +518,9 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     constexpr int DR = DK + DV, LD = DR + 8;                 // a shared-memory row: key, value, 16 bytes of padding
     extern __shared__ __align__(16) uint8_t br_smem[];
     __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(br_smem);      // [2][BR_K][LD]
+    // the bias of the distances a tile's keys can have from the block's queries, staged per tile: element x is the
+    // bias at distance (pos0 - tile's first position - (BR_K - 1)) + x, clamped into the table
+    __shared__ float s_bias[2][BR_Q + BR_K];
     const int seq = blockIdx.y, h = blockIdx.z;
     const int t0 = cu_seqlens[seq], n_run = cu_seqlens[seq + 1] - t0;
     const int a0 = blockIdx.x * BR_Q;                        // first query of the block within the run
@@ -305,6 +548,10 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
             br_copy16(dst + r * LD + k * 8, src + r * DR + k * 8);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        if (bias_t != nullptr && threadIdx.x < BR_Q + BR_K - 1) {
+            const int d = pos0 - pg * BR_K - (BR_K - 1) + (int)threadIdx.x;
+            s_bias[stage][threadIdx.x] = __ldg(bias_t + (size_t)h * (far + 1) + min(max(d, 0), far));
+        }
     };
     load_tile(0, 0);
 
@@ -322,7 +569,7 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
             qf[ks][3] = r_hi < n_q ? *reinterpret_cast<const uint32_t*>(q_hi + ks * 16 + 8) : 0u;
         }
     }
-    const float* bias_h = bias_t ? bias_t + (size_t)h * (far + 1) : nullptr;
+    const bool biased = bias_t != nullptr;
     const float sink_h = sink ? sink[h] : -INFINITY;
     float m_lo = sink_h, m_hi = sink_h, l_lo = 0.f, l_hi = 0.f;
     float o[DV / 8][4];
@@ -359,6 +606,8 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                 }
             }
             // scale, bias, mask; the rows' maxima
+            const float* sb = s_bias[stage];
+            const int d_min = pos0 - p_base - (BR_K - 1);
             float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
             for (int n = 0; n < BR_K / 8; ++n) {
@@ -369,7 +618,7 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                     const int d = i - p;
                     const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
                     float v = s[n][c] * scale;
-                    if (bias_h && see) v += __ldg(bias_h + min(d, far));
+                    if (biased) v += sb[min(max(d - d_min, 0), BR_Q + BR_K - 2)];
                     v = see ? v : -INFINITY;
                     s[n][c] = v;
                     if (c & 2) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
@@ -381,15 +630,16 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
             const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
             const float u_lo = mn_lo == -INFINITY ? 0.f : mn_lo, u_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-            const float c_lo = expf(m_lo - u_lo), c_hi = expf(m_hi - u_hi);      // exp(-inf) = 0 before the first key
+            const float c_lo = __expf(m_lo - u_lo), c_hi = __expf(m_hi - u_hi);  // exp(-inf) = 0 before the first key
             m_lo = mn_lo; m_hi = mn_hi;
             l_lo *= c_lo; l_hi *= c_hi;
 #pragma unroll
             for (int n = 0; n < DV / 8; ++n) { o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi; }
 #pragma unroll
             for (int n = 0; n < BR_K / 8; ++n) {
-                s[n][0] = expf(s[n][0] - u_lo); s[n][1] = expf(s[n][1] - u_lo);
-                s[n][2] = expf(s[n][2] - u_hi); s[n][3] = expf(s[n][3] - u_hi);
+                // the weights keep eight bits as the second product's operand: the fast exponential does
+                s[n][0] = __expf(s[n][0] - u_lo); s[n][1] = __expf(s[n][1] - u_lo);
+                s[n][2] = __expf(s[n][2] - u_hi); s[n][3] = __expf(s[n][3] - u_hi);
                 l_lo += s[n][0] + s[n][1];
                 l_hi += s[n][2] + s[n][3];
             }

@@ -76,19 +76,31 @@ def attention_runs(q: torch.Tensor, cache: torch.Tensor, bias_t: Optional[torch.
     return out
 
 
-def splits_for(n_tokens: int, heads: int, longest: int, device) -> int:
-    """Ranges the visible keys of a (token, head) are cut into: a step of few tokens is cut until a block has about
-    64 keys or the launch fills the GPU three times over; prompts are not cut.  The ranges are joined in range
-    order, so a launch shape always gives the same bits; logits agree across shapes to rounding."""
+def group_heads(dtype: torch.dtype, dk: int, dv: int, per_kv: int) -> int:
+    """Query heads of one key/value head that a block of the grouped token form keeps (it reads every cached row
+    once for all of them); 0: this shape takes the form with a block per head (float32, sizes other than 32, 64,
+    128; TQ_BIAS_NO_GROUP=1)."""
+    import os
+    if dtype != torch.bfloat16 or os.environ.get("TQ_BIAS_NO_GROUP", "") not in ("", "0"):
+        return 0
+    return int(load_kernel(_LIB).tq_bias_attention_group_heads(c_int(dk), c_int(dv), c_int(per_kv)))
+
+
+def splits_for(n_tokens: int, blocks_per_token: int, longest: int, device) -> int:
+    """Ranges the visible keys of a token are cut into: a step of few tokens is cut until a block has about 64 keys
+    or the launch fills the GPU three times over (four blocks of four warps an SM); prompts are not cut.  The
+    ranges are joined in range order, so a launch shape always gives the same bits; logits agree across shapes to
+    rounding."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return int(max(1, min(64, longest // 64, (12 * sms) // max(1, n_tokens * heads))))
+    return int(max(1, min(64, longest // 64, (12 * sms) // max(1, n_tokens * blocks_per_token))))
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, bias: Optional[torch.Tensor], sink: Optional[torch.Tensor],
               positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, page_size: int,
               window: int, keep_first: int, scale: float, out: torch.Tensor, heads: int, kv_heads: int, dk: int,
-              dv: int, n_splits: int = 1) -> torch.Tensor:
-    """Every (token, head) on its own over its sequence's cache.  q [T, heads, dk]; out [T, heads * dv]; bias float32
+              dv: int, n_splits: int = 1, bias_t: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Every (token, head) on its own over its sequence's cache; with bias_t (the bias as [heads, far + 1]) given or
+    no bias at all, and a shape the grouped form is built for, a block per (token, key/value head) instead.  q [T, heads, dk]; out [T, heads * dv]; bias float32
     [far + 1, heads], row min(distance, far) added to the scaled score (None: no bias); sink float32 [heads]: exp(sink)
     joins the softmax's denominator (None: an ordinary softmax); window 0: every earlier position is seen, else the
     last `window` and the first `keep_first`."""
@@ -105,6 +117,13 @@ def attention(q: torch.Tensor, cache: torch.Tensor, bias: Optional[torch.Tensor]
         want_f32(sink, "the sink")
     partial = torch.empty(T * heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
     lib = load_kernel(_LIB)
+    if (bias is None or bias_t is not None) and page_size % 8 == 0 and group_heads(q.dtype, dk, dv, heads // kv_heads):
+        check(_LIB, lib.tq_bias_attention_group(
+            ptr(q), ptr(cache), ptr(bias_t), c_int(far), ptr(sink), ptr(positions), ptr(seq_of_token), ptr(page_table),
+            c_int(page_table.shape[1]), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), ptr(out),
+            ptr(partial), c_int(n_splits), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+            c_int(page_table.shape[0]), c_int(cache.shape[0]), stream()), kernels=2 if n_splits > 1 else 1)
+        return out
     check(_LIB, lib.tq_bias_attention(
         ptr(q), ptr(cache), c_int(code(q.dtype)), ptr(bias), c_int(far), ptr(sink), ptr(positions), ptr(seq_of_token),
         ptr(page_table), c_int(page_table.shape[1]), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale),

@@ -139,9 +139,12 @@ class BiasedWindowAttentionMixer(Mixer):
                               self.heads, self.kv_heads, self.dim, self.vdim)
         else:
             longest = min(self.window + self.keep_first, ctx.max_kv_len) if self.window else ctx.max_kv_len
+            per_kv = self.heads // self.kv_heads
+            gc = KB.group_heads(act, self.dim, self.vdim, per_kv)
+            blocks = self.kv_heads * -(-per_kv // gc) if gc else self.heads
             KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                          cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
-                         self.dim, self.vdim, n_splits=KB.splits_for(T, self.heads, longest, dev))
+                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev), bias_t=self.bias_t)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
 
