@@ -184,3 +184,41 @@ def test_cache_write_and_both_attention_kernels(case, dtype):
     p = np.exp(s - s.max())
     row = (p / p.sum()) @ v[:, a // (H // G)]
     assert np.abs(out[i].float().cpu().numpy().reshape(H, dv)[a] - row).max() < tol * max(1.0, np.abs(row).max()) * 3
+
+
+@pytest.mark.parametrize("T,E,k,groups,keep,H", [(1, 12, 3, 3, 2, 64), (8, 60, 4, 4, 2, 128), (5, 8, 8, 1, 1, 40), (24, 16, 2, 8, 3, 72)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_one_launch_router_chooses_like_the_separate_kernels(T, E, k, groups, keep, H, dtype):
+    """Decode steps take logits, corrected selection, layout and the rows' copies in one launch: the same choices,
+    weights and layout as the separate kernels give."""
+    from turboquant_cpp_b200.kernels import elementwise as KE, moe as KM
+    rng = np.random.default_rng(T * 100 + E)
+    x = dev(rng.standard_normal((T, H)), dtype)
+    wr = dev(0.3 * rng.standard_normal((E, H)), dtype)
+    sg = dev(rng.standard_normal((1, H)), dtype)
+    corr = dev(0.3 / E * rng.standard_normal(E), torch.float32)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    f32 = dict(dtype=torch.float32, device=DEV)
+    ids_a, w_a, s_a = torch.empty((T, k), **i32), torch.empty((T, k), **f32), torch.empty((T,), **f32)
+    ids_b, w_b, s_b = torch.empty((T, k), **i32), torch.empty((T, k), **f32), torch.empty((T,), **f32)
+    logits = KM.router_logits(x, wr, sg, torch.empty((T, E + 1), **f32))
+    KM.router_select_corrected(logits, corr, k, True, P.WEIGHT_FLOOR, groups, keep, ids_a, w_a, s_a)
+    lay_a = KM.ExpertLayout(T * k, E, 16, DEV)
+    KM.moe_align(ids_a, lay_a)
+    rows_a = KE.gather_rows(x, lay_a.sorted_pair, k, torch.empty((T * k, H), dtype=dtype, device=DEV))
+    lay_b = KM.ExpertLayout(T * k, E, 16, DEV)
+    rows_b = torch.empty((T * k, H), dtype=dtype, device=DEV)
+    KM.router_small(x, wr, sg, k, True, ids_b, w_b, s_b, lay_b, rows_b, correction=corr, corrected=True,
+                    floor=P.WEIGHT_FLOOR, n_groups=groups, keep_groups=keep)
+    assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b) and torch.equal(s_a, s_b)
+    assert torch.equal(lay_a.sorted_pair[:T * k], lay_b.sorted_pair[:T * k]) and torch.equal(lay_a.row_of_pair[:T * k], lay_b.row_of_pair[:T * k])
+    n = int(lay_a.n_tiles.item())
+    assert n == int(lay_b.n_tiles.item()) and torch.equal(lay_a.tile_expert[:n], lay_b.tile_expert[:n])
+    assert torch.equal(rows_a, rows_b)
+    # and against the plain choice, where its margin is clear
+    margins = []
+    w = {"router": wr.float().cpu().numpy().astype(np.float64), "correction": corr.cpu().numpy().astype(np.float64)}
+    ids, _ = P.route(x.float().cpu().numpy().astype(np.float64), w, {"experts": E, "top": k, "groups": {"count": groups, "keep": keep}}, margins=margins)
+    for t in range(T):
+        if margins[t] > 1e-5:
+            assert sorted(ids_b[t].tolist()) == sorted(ids[t].tolist())

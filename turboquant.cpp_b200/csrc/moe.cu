@@ -273,25 +273,12 @@ TQ_EXPORT int tq_router_select(float* logits, int* ids, float* wts, float* share
     return 0;
 }
 
-// Selection with a correction of the choice and groups of experts, one warp per token.  s = softmax(logits) over all
-// E experts; the choice looks at c = s + correction (correction may be null: c = s); with n_groups > 1 the experts form
-// n_groups equal groups of neighbours, a group's value is its largest c, and only experts of the keep_groups groups
-// with the largest values can be chosen (the others count as minus infinity); the k largest c are chosen (ties to
-// the lowest index); the weights are the chosen experts' s, divided by (their sum + floor) if renorm.
-// choice: T * E floats of scratch; group_best: T * n_groups floats of scratch (n_groups > 1).
-__global__ void router_select_corrected_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
-                                               float* __restrict__ choice, float* __restrict__ group_best,
-                                               int* __restrict__ ids, float* __restrict__ wts,
-                                               float* __restrict__ shared_scale, int T_, int E, int k, int renorm,
-                                               float floor_, int n_groups, int keep_groups) {
-    tq_grid_wait();                    // everything below may read what the previous kernel wrote
-    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= T_) return;
-    const float* row = logits + (size_t)t * (E + 1);
-    float* c = choice + (size_t)t * E;
-    if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
+// The selection for one row by one warp (see router_select_corrected_kernel): row: E logits; c: E floats and gb:
+// n_groups floats of scratch (global or shared memory).
+__device__ __forceinline__ void select_corrected_row(const float* row, const float* __restrict__ correction, float* c,
+                                                     float* gb, int* __restrict__ ids_row, float* __restrict__ wts_row,
+                                                     int E, int k, int renorm, float floor_, int n_groups,
+                                                     int keep_groups, int lane) {
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
     mx = tq_warp_max(mx);
@@ -302,7 +289,6 @@ __global__ void router_select_corrected_kernel(const float* __restrict__ logits,
     __syncwarp();
     if (n_groups > 1) {
         const int per = E / n_groups;
-        float* gb = group_best + (size_t)t * n_groups;
         for (int g = lane; g < n_groups; g += 32) {
             float b = -INFINITY;
             for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
@@ -347,16 +333,39 @@ __global__ void router_select_corrected_kernel(const float* __restrict__ logits,
         const float p = found ? expf(row[best_e] - mx) / sum : 0.f;
         picked_sum += p;                         // identical in every lane
         if (lane == 0) {
-            ids[(size_t)t * k + j] = best_e;
-            wts[(size_t)t * k + j] = p;
+            ids_row[j] = best_e;
+            wts_row[j] = p;
             if (found) c[best_e] = -INFINITY;
         }
         __syncwarp();
     }
     if (renorm) {
         __syncwarp();
-        for (int j = lane; j < k; j += 32) wts[(size_t)t * k + j] = wts[(size_t)t * k + j] / (picked_sum + floor_);
+        for (int j = lane; j < k; j += 32) wts_row[j] = wts_row[j] / (picked_sum + floor_);
     }
+}
+
+// Selection with a correction of the choice and groups of experts, one warp per token.  s = softmax(logits) over all
+// E experts; the choice looks at c = s + correction (correction may be null: c = s); with n_groups > 1 the experts form
+// n_groups equal groups of neighbours, a group's value is its largest c, and only experts of the keep_groups groups
+// with the largest values can be chosen (the others count as minus infinity); the k largest c are chosen (ties to
+// the lowest index); the weights are the chosen experts' s, divided by (their sum + floor) if renorm.
+// choice: T * E floats of scratch; group_best: T * n_groups floats of scratch (n_groups > 1).
+__global__ void router_select_corrected_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                               float* __restrict__ choice, float* __restrict__ group_best,
+                                               int* __restrict__ ids, float* __restrict__ wts,
+                                               float* __restrict__ shared_scale, int T_, int E, int k, int renorm,
+                                               float floor_, int n_groups, int keep_groups) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T_) return;
+    const float* row = logits + (size_t)t * (E + 1);
+    float* c = choice + (size_t)t * E;
+    if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
+    select_corrected_row(row, correction, c, group_best ? group_best + (size_t)t * n_groups : nullptr, ids + (size_t)t * k,
+                         wts + (size_t)t * k, E, k, renorm, floor_, n_groups, keep_groups, lane);
 }
 
 TQ_EXPORT int tq_router_select_corrected(const float* logits, const float* correction, float* choice, float* group_best,
@@ -899,7 +908,8 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
                     int* __restrict__ counts, int* __restrict__ sorted_pair, int* __restrict__ row_of_pair,
                     int* __restrict__ expert_offset, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                     int* __restrict__ tile_count, int* __restrict__ n_tiles, TA* __restrict__ x_rows, int vec_x,
-                    int* __restrict__ counter) {
+                    int* __restrict__ counter, const float* __restrict__ correction, int corrected, float floor_,
+                    int n_groups, int keep_groups) {
     tq_grid_wait();
     tq_grid_launch_dependents();
     extern __shared__ float s_dyn[];
@@ -942,7 +952,11 @@ router_small_kernel(const TA* __restrict__ x, const TW* __restrict__ wr, const T
     // ---- selection: warp 0 (the same choices and weights as router_select_kernel) ----
     if (warp == 0) {
         if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-s_logit[E]));
-        if (E <= 32 * SELECT_REGS) {
+        if (corrected) {
+            // corrected scores and groups: the row's place (no longer needed) is the scratch, E + n_groups <= H floats
+            select_corrected_row(s_logit, correction, s_x, s_x + E, ids + (size_t)t * k, wts + (size_t)t * k, E, k, renorm,
+                                 floor_, n_groups, keep_groups, lane);
+        } else if (E <= 32 * SELECT_REGS) {
             select_in_registers(s_logit, E, k, renorm, lane, ids + (size_t)t * k, wts + (size_t)t * k, nullptr);
         } else {
             float mx = -INFINITY;
@@ -1031,8 +1045,15 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
                               int* ids, float* wts, float* shared_scale, int tile_rows, int* counts, int* sorted_pair,
                               int* row_of_pair, int* expert_offset, int* tile_expert, int* tile_row0, int* tile_count,
                               int* n_tiles, void* x_rows, int* counter, int T_, int H, int E, int k, int renorm,
+                              const float* correction, int corrected, float floor_, int n_groups, int keep_groups,
                               cudaStream_t stream) {
     if (T_ == 0) return 0;
+    if (corrected) {            // corrected scores, groups, a floor under the weights' sum: the counter form knows them
+        TQ_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+                   (n_groups == 1 || keep_groups * (E / n_groups) >= k), "router_small: %d of %d groups of %d experts for %d choices",
+                   keep_groups, n_groups, E / (n_groups > 0 ? n_groups : 1), k);
+        TQ_REQUIRE(E + n_groups <= H, "router_small: %d experts and %d groups need scratch of a row of %d values", E, n_groups, H);
+    }
     TQ_REQUIRE(T_ * k <= SMALL_MAX_PAIRS && E <= SMALL_MAX_EXPERTS,
                "router_small: %d pairs / %d experts exceed %d / %d", T_ * k, E, SMALL_MAX_PAIRS, SMALL_MAX_EXPERTS);
     TQ_REQUIRE(E >= 1 && k >= 1 && k <= E && tile_rows >= 1, "router_small: bad sizes E=%d k=%d tile_rows=%d", E, k, tile_rows);
@@ -1052,7 +1073,7 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
         const char* tiny_env = getenv("TQ_ROUTER_NO_TINY");
         const bool no_tiny = tiny_env && tiny_env[0] && tiny_env[0] != '0';
         const size_t smem_tiny = (size_t)T_ * H * 2 + (size_t)T_ * (E + 1) * 4;
-        if (!no_tiny && (T_ == 1 || (tiny_env && tiny_env[0] == '0' && T_ <= TINY_MAX_T)) && T_ * k <= TINY_MAX_PAIRS && T_ <= tile_rows && act_dtype == TQ_BF16 && w_dtype == TQ_BF16 &&
+        if (!corrected && !no_tiny && (T_ == 1 || (tiny_env && tiny_env[0] == '0' && T_ <= TINY_MAX_T)) && T_ * k <= TINY_MAX_PAIRS && T_ <= tile_rows && act_dtype == TQ_BF16 && w_dtype == TQ_BF16 &&
             H % 8 == 0 && vec_w && vec_x && E <= 32 * SELECT_REGS && smem_tiny <= 40 * 1024) {
 #define TINY_CASE(TT) case TT: tq_launch(1, TINY_THREADS, smem_tiny, stream)(router_tiny_kernel<TT>, (const __nv_bfloat16*)x, \
             (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, ids, wts, shared_scale, H, E, k, renorm, counts, sorted_pair,  \
@@ -1066,7 +1087,7 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
     // the cluster form (TQ_ROUTER_NO_CLUSTER=1: the counter form after all)
     const size_t smem_cluster = (((size_t)(E + 1) * 4 + 15) & ~(size_t)15) + (size_t)T_ * H * abytes;
     const char* no_cluster = getenv("TQ_ROUTER_NO_CLUSTER");
-    const bool cluster = T_ <= SMALL_CLUSTER && E <= 32 * SELECT_REGS && smem_cluster <= SMALL_CLUSTER_DYNAMIC_BYTES &&
+    const bool cluster = !corrected && T_ <= SMALL_CLUSTER && E <= 32 * SELECT_REGS && smem_cluster <= SMALL_CLUSTER_DYNAMIC_BYTES &&
                          (vec_x || !vec_w) &&       // the order of a sum follows the weights' loads; the rows must allow the same
                          !(no_cluster && no_cluster[0] && no_cluster[0] != '0');
     if (cluster) {
@@ -1081,7 +1102,8 @@ TQ_EXPORT int tq_router_small(const void* x, int act_dtype, const void* wr, cons
         TQ_DISPATCH(act_dtype, TA, TQ_DISPATCH(w_dtype, TW,
             (tq_launch(T_, SMALL_THREADS, smem, stream)(router_small_kernel<TA, TW>, (const TA*)x, (const TW*)wr, (const TW*)wsg,
                 ids, wts, shared_scale, T_, H, E, k, renorm, vec_w, tile_rows, counts, sorted_pair, row_of_pair, expert_offset,
-                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter))));
+                tile_expert, tile_row0, tile_count, n_tiles, (TA*)x_rows, vec_x, counter, correction, corrected, floor_,
+                n_groups, keep_groups))));
     }
     TQ_CHECK_LAUNCH("router_small");
     return 0;

@@ -136,10 +136,12 @@ def _counter(device: torch.device) -> torch.Tensor:
 
 def router_small(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top_k: int,
                  renorm: bool, ids: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
-                 layout: ExpertLayout, x_rows: torch.Tensor) -> None:
+                 layout: ExpertLayout, x_rows: torch.Tensor, correction: Optional[torch.Tensor] = None,
+                 corrected: bool = False, floor: float = 0.0, n_groups: int = 1, keep_groups: int = 1) -> None:
     """For steps of few tokens: router, expert-sorted layout and the sorted copies of the token rows
     (x_rows[row] = x[token of that row]) in one launch.  Launches on one device must not overlap (they share
-    the counter that tells the last block its turn)."""
+    the counter that tells the last block its turn).  corrected: the selection of router_select_corrected
+    (correction [E] float32 or None, groups, floor); it needs n_experts + n_groups <= hidden."""
     T, H = x.shape
     E = w_router.shape[0]
     want_int32(ids, "expert ids")
@@ -153,7 +155,8 @@ def router_small(x: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optiona
         ptr(ids), ptr(weights), ptr(shared_scale), c_int(lo.tile_rows), ptr(lo.counts), ptr(lo.sorted_pair),
         ptr(lo.row_of_pair), ptr(lo.expert_offset), ptr(lo.tile_expert), ptr(lo.tile_row0), ptr(lo.tile_count),
         ptr(lo.n_tiles), ptr(x_rows), ptr(_counter(x.device)), c_int(T), c_int(H), c_int(E), c_int(top_k),
-        c_int(1 if renorm else 0), stream()))
+        c_int(1 if renorm else 0), ptr(correction), c_int(1 if corrected else 0), c_float(floor), c_int(n_groups),
+        c_int(keep_groups), stream()))
 
 
 def moe_align(ids: torch.Tensor, layout: ExpertLayout) -> None:

@@ -26,6 +26,7 @@ from typing import List, Optional
 import torch
 
 from ..kernels import bias_attention as KB
+from ..kernels import gemv as KG
 from ..kernels.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 from .base import KVNeed, LayerCache, Mixer, StepContext, register_mixer
@@ -104,7 +105,7 @@ class BiasedWindowAttentionMixer(Mixer):
             self.mix = float(store.get(p + "vmix").float().item())
 
     def kernels(self) -> List[str]:
-        return ["bias_attention"]
+        return ["bias_attention"] + (["gemv"] if getattr(self, "run_dtype", None) == torch.bfloat16 else [])
 
     def cache_need(self) -> KVNeed:
         return KVNeed(self.kv_heads, self.dim + self.vdim, self.window, planes=1, keep_first=self.keep_first)
@@ -145,6 +146,8 @@ class BiasedWindowAttentionMixer(Mixer):
             KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                          cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
                          self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev), bias_t=self.bias_t)
+        if KG.pays(o, self.w_o):                   # a few tokens: the output projection as a stream of its weights
+            return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
         return linear(o, self.w_o, out_dtype=torch.float32)
 
 

@@ -246,7 +246,7 @@ class MoEFeedForward(FeedForward):
         scale = torch.empty((T,), dtype=torch.float32, device=dev) if self.w_shared_gate is not None else None
         layout = KM.ExpertLayout(T * k, self.n_experts, tile or KM.TILE_ROWS, dev)
         x_rows = torch.empty((T * k, H), dtype=xn.dtype, device=dev)
-        small = KM.router_small_pays(T, k, self.n_experts, H) and not self.corrected
+        small = KM.router_small_pays(T, k, self.n_experts, H) and (not self.corrected or self.n_experts + self.n_groups <= H)
         # Decode steps whose pairs reach the number of experts (most experts are read: the routed products are several
         # times the shared expert's): the router first, alone on the GPU, then the shared expert beside the routed
         # ones with its down projection's K shared out.  With fewer pairs the shared expert starts first and the
@@ -289,7 +289,9 @@ class MoEFeedForward(FeedForward):
             shared_expert()
         if small:
             # few tokens (decoding): router, layout and the sorted copies of the rows in one launch
-            KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows)
+            KM.router_small(xn, self.w_router, self.w_shared_gate, k, self.norm_topk, ids, wts, scale, layout, x_rows,
+                            correction=self.w_correction, corrected=self.corrected, floor=self.renorm_floor,
+                            n_groups=self.n_groups, keep_groups=self.keep_groups)
         else:
             if self.w_router_packed is not None and T >= self.ROUTER_TC_MIN_TOKENS:
                 # long steps (prompts): the logits of all tokens as one tensor-core product (bf16 x bf16 products
