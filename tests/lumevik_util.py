@@ -177,18 +177,20 @@ def run_steps_with_routing(engine, steps, ends, leave_open=False):
 
 # below this gap between the last chosen and the first dropped score another choice is as right (the scores are
 # probabilities: of order 1 / experts)
-FLIP_MARGIN = {"float32": 1e-5, "bfloat16": 2e-2}
+FLIP_MARGIN = {"float32": 1e-5, "bfloat16": 4e-2}
 
 
 def check_against_plain(plain, tokens, logits, routing, dtype, what):
-    """The engine's logits {position: row} against the plain model.  Where the engine chose other experts than the
-    plain model, the plain model's own margin there must be tiny and such places rare; the logits are then held
-    against the plain model run with the engine's choices."""
+    """The engine's logits {position: row} against the plain model.  Routed layer by routed layer: where the engine
+    chose other experts than the plain model (run with the engine's choices in the layers before), the plain
+    model's own margin there must be tiny and such places rare; the logits are then held against the plain model
+    run with the engine's choices."""
     n = len(tokens)
     rec = []
     ref = plain.forward(list(tokens), routing=rec)
-    flips, forced = 0, []
-    for li, (ids, _, margins) in enumerate(rec):
+    flips, forced, li = 0, [], 0
+    while li < len(rec):
+        ids, _, margins = rec[li]
         got = routing[li]
         assert sorted(got) == list(range(n)), f"{what}: routed layer {li} did not see every position exactly once"
         eng = np.stack([got[p] for p in range(n)])
@@ -198,6 +200,10 @@ def check_against_plain(plain, tokens, logits, routing, dtype, what):
                                                      f"plain {ids[p].tolist()} with margin {margins[p]:.3e}")
         flips += len(differ)
         forced.append(eng)
+        li += 1
+        if len(differ) and li < len(rec):         # the later layers see what the engine's choice made of this one
+            rec = []
+            ref = plain.forward(list(tokens), routing=rec, forced=forced)
     assert flips <= max(2, n * max(1, len(rec)) // 20), f"{what}: {flips} expert choices differ"
     if flips:
         ref = plain.forward(list(tokens), forced=forced)

@@ -224,7 +224,8 @@ class PlainLumevik:
     def forward(self, tokens, streams=None, routing=None, forced=None):
         """Logits [T, vocab] of one sequence; `streams` collects the residual stream after every layer, `routing`
         (experts, weights, margins) of every routed layer, in layer order; forced: per routed layer, in that order,
-        the experts [T, top] to take instead of the model's own choice."""
+        the experts [T, top] to take instead of the model's own choice (None, or a shorter list: the layers without
+        an entry choose for themselves)."""
         t, cfg, eps = self.t, self.cfg, self.eps
         x = t["embed"][np.asarray(tokens)].astype(F)
         v_first = None
@@ -248,7 +249,7 @@ class PlainLumevik:
                     y = dense_ff(h, {n: t[p + "mlp." + n] for n in ("gate", "up", "down")}, mlp["limit"])
                 else:
                     margins = []
-                    y, ids, wts = moe_ff(h, t, p + "mlp.", mlp, None if forced is None else forced[n_routed], margins)
+                    y, ids, wts = moe_ff(h, t, p + "mlp.", mlp, None if forced is None or n_routed >= len(forced) else forced[n_routed], margins)
                     n_routed += 1
                     if routing is not None:
                         routing.append((ids, wts, np.array(margins)))

@@ -236,12 +236,17 @@ TQ_EXPORT int tq_bias_attention(const void* q, const void* cache, int act_dtype,
 // Token form for grouped queries, bfloat16, key and value sizes of 32, 64 or 128: grid (token x head chunks, kv head,
 // range), 4 warps.  A block keeps up to GC query heads of one key/value head in registers and reads every cached row
 // once for all of them: a row's key is read by LPK = DK / 8 lanes with one 16-byte load each, so a warp covers
-// 32 / LPK rows per instruction and eight rows per iteration, the next iteration's loads in flight during this
-// one's arithmetic; the value's 16-byte pieces are shared out over the same lanes.  Online softmax per head and
+// 32 / LPK rows per instruction and eight rows per iteration; the value's 16-byte pieces are shared out over the same
+// lanes.  The loads are cp.async copies into a ring in shared memory, two iterations ahead of the one being computed,
+// every lane copying and reading back only its own 16 bytes (no barrier between the lanes or warps).  Online softmax per head and
 // lane group (fp32), merged over the lane groups by shuffles and over the warps through shared memory, in a fixed
 // order.  The ranges' states go to `partial` as in the form above and are joined by the same merge.
 // bias_t: [heads][far + 1].
 // ---------------------------------------------------------------------------------------
+#define BG_STAGES 3
+__device__ __forceinline__ void br_copy16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
 struct BaRaw { uint4 v; };
 __device__ __forceinline__ BaRaw ba_fetch(const __nv_bfloat16* p) { BaRaw r; r.v = *reinterpret_cast<const uint4*>(p); return r; }
 __device__ __forceinline__ void ba_widen(const BaRaw& r, float (&f)[8]) {
@@ -278,21 +283,32 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int n0 = split * per, n1 = min(span.count, n0 + per);
     const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
 
-    BaRaw kr[LOADS], vr[LOADS][NVC];
-    auto fetch_group = [&](int base) {
+    // the ring: [warp][stage][a key and NVC value pieces per load][lane] of 16 bytes, a lane's own slots only
+    constexpr int SLOTS = LOADS * (1 + NVC);
+    extern __shared__ __align__(16) uint4 ba_ring[];
+    uint4* ring = ba_ring + (size_t)warp * BG_STAGES * SLOTS * 32 + lane;
+    auto copy_group = [&](int base, int stage) {
+        uint4* dst = ring + (size_t)stage * SLOTS * 32;
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int n = min(base + j * KPI + part, n1 - 1);            // rows past the range repeat its last row (masked below)
             const int p = span.at(n);
             const int page = TQ_CHECKED(table[TQ_CHECKED(p / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
             const __nv_bfloat16* row = cache + (((size_t)page * nkv + g) * page_size + p % page_size) * DR;
-            kr[j] = ba_fetch(row + sub * 8);
+            br_copy16(dst + (j * (1 + NVC)) * 32, row + sub * 8);
 #pragma unroll
             for (int c = 0; c < NVC; ++c)
-                if (sub + c * LPK < NV8) vr[j][c] = ba_fetch(row + DK + (sub + c * LPK) * 8);
+                if (sub + c * LPK < NV8) br_copy16(dst + (j * (1 + NVC) + 1 + c) * 32, row + DK + (sub + c * LPK) * 8);
         }
     };
-    if (n0 + warp * GS < n1) fetch_group(n0 + warp * GS);
+    int next_base = n0 + warp * GS, next_stage = 0, stage = 0;
+#pragma unroll
+    for (int i = 0; i < BG_STAGES - 1; ++i) {                 // one commit per group, also past the end: the count is uniform
+        if (next_base < n1) copy_group(next_base, next_stage);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        next_base += BA_WARPS * GS;
+        next_stage = next_stage + 1 == BG_STAGES ? 0 : next_stage + 1;
+    }
 
     float qv[GC][8], acc[GC][NVC][8], m[GC], l[GC];
 #pragma unroll
@@ -309,20 +325,29 @@ bias_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
             for (int i = 0; i < 8; ++i) acc[h][c][i] = 0.f;
     }
     for (int base = n0 + warp * GS; base < n1; base += BA_WARPS * GS) {
+        // the slot filled now was read one iteration ago, and what was read there has been used since
+        if (next_base < n1) copy_group(next_base, next_stage);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        next_base += BA_WARPS * GS;
+        next_stage = next_stage + 1 == BG_STAGES ? 0 : next_stage + 1;
+        asm volatile("cp.async.wait_group %0;" ::"n"(BG_STAGES - 1) : "memory");   // all but the newest groups have landed: this one has
+        const uint4* src = ring + (size_t)stage * SLOTS * 32;
+        stage = stage + 1 == BG_STAGES ? 0 : stage + 1;
         float kf[LOADS][8], vf[LOADS][NVC][8];
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
-            ba_widen(kr[j], kf[j]);
+            BaRaw r;
+            r.v = src[(j * (1 + NVC)) * 32];
+            ba_widen(r, kf[j]);
 #pragma unroll
             for (int c = 0; c < NVC; ++c) {
-                if (sub + c * LPK < NV8) ba_widen(vr[j][c], vf[j][c]);
+                if (sub + c * LPK < NV8) { r.v = src[(j * (1 + NVC) + 1 + c) * 32]; ba_widen(r, vf[j][c]); }
                 else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) vf[j][c][i] = 0.f;
                 }
             }
         }
-        if (base + BA_WARPS * GS < n1) fetch_group(base + BA_WARPS * GS);      // the next rows fly during this group's math
         float s[LOADS][GC];
 #pragma unroll
         for (int j = 0; j < LOADS; ++j)
@@ -451,7 +476,16 @@ TQ_EXPORT int tq_bias_attention_group(const void* q, const void* cache, const fl
     bool done = false;
 #define BG_CASE(DK_, DV_, GC_)                                                                                        \
     if (!done && dk == DK_ && dv == DV_ && gc == GC_) {                                                               \
-        tq_launch(grid, BA_WARPS * 32, 0, stream)(bias_attention_group_kernel<DK_, DV_, GC_>, (const __nv_bfloat16*)q,  \
+        constexpr int kpi = 32 / (DK_ / 8), loads = kpi >= 8 ? 1 : 8 / kpi, nvc = DV_ / 8 > DK_ / 8 ? DV_ / DK_ : 1;   \
+        constexpr int ring_bytes = BA_WARPS * BG_STAGES * loads * (1 + nvc) * 32 * 16;                                \
+        static bool configured = false;                                                                               \
+        if (!configured) {                                                                                            \
+            cudaError_t e = cudaFuncSetAttribute(bias_attention_group_kernel<DK_, DV_, GC_>,                           \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes);            \
+            if (e != cudaSuccess) TQ_FAIL(-1, "bias_attention_group: %d bytes of shared memory refused: %s", ring_bytes, cudaGetErrorString(e)); \
+            configured = true;                                                                                        \
+        }                                                                                                             \
+        tq_launch(grid, BA_WARPS * 32, ring_bytes, stream)(bias_attention_group_kernel<DK_, DV_, GC_>, (const __nv_bfloat16*)q,  \
             (const __nv_bfloat16*)cache, bias_t, far, sink, positions, seq_of_token, page_table, table_stride, page_size, \
             window, keep_first, scale, (__nv_bfloat16*)out, partial, n_splits, nh, nkv, n_seqs, n_pages);             \
         done = true;                                                                                                  \
@@ -498,9 +532,6 @@ __device__ __forceinline__ void br_mma(float (&d)[4], const uint32_t (&a)[4], ui
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void br_copy16(void* smem_dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
-}
 __device__ __forceinline__ uint32_t br_pack(float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -521,9 +552,12 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     // the bias of the distances a tile's keys can have from the block's queries, staged per tile: element x is the
     // bias at distance (pos0 - tile's first position - (BR_K - 1)) + x, clamped into the table
     __shared__ float s_bias[2][BR_Q + BR_K];
-    const int seq = blockIdx.y, h = blockIdx.z;
+    // the grid is (head, sequence, block of queries from the last to the first): blocks start in that order, so the
+    // blocks with the most pages to walk (late queries) run first and the short ones fill the GPU's last round, and
+    // the heads that share a key/value head run side by side and meet in the L2
+    const int seq = blockIdx.y, h = blockIdx.x;
     const int t0 = cu_seqlens[seq], n_run = cu_seqlens[seq + 1] - t0;
-    const int a0 = blockIdx.x * BR_Q;                        // first query of the block within the run
+    const int a0 = (int)(gridDim.z - 1 - blockIdx.z) * BR_Q; // first query of the block within the run
     if (a0 >= n_run) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = h / (nh / nkv);
@@ -691,7 +725,7 @@ int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int 
         if (e != cudaSuccess) TQ_FAIL(-1, "bias_attention_runs: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((max_run + BR_Q - 1) / BR_Q, n_seqs, nh);
+    dim3 grid(nh, n_seqs, (max_run + BR_Q - 1) / BR_Q);
     tq_launch(grid, BR_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far,
         sink, cu_seqlens, seq_start, page_table, table_stride, window, keep_first, scale, (__nv_bfloat16*)out, nh, nkv, n_pages);
     return 0;
@@ -707,7 +741,7 @@ TQ_EXPORT int tq_bias_attention_runs(const void* q, const void* cache, int act_d
     TQ_REQUIRE(act_dtype == TQ_BF16, "bias_attention_runs: bfloat16 only");
     TQ_REQUIRE(page_size == BR_K, "bias_attention_runs: pages of %d positions, not %d", BR_K, page_size);
     TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "bias_attention_runs: %d heads are not a multiple of %d key/value heads", nh, nkv);
-    TQ_REQUIRE(nh <= 65535 && n_seqs <= 65535, "bias_attention_runs: %d heads or %d sequences exceed the grid limit", nh, n_seqs);
+    TQ_REQUIRE(n_seqs <= 65535 && (max_run + BR_Q - 1) / BR_Q <= 65535, "bias_attention_runs: %d sequences or runs of %d tokens exceed the grid limit", n_seqs, max_run);
     TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_runs: negative window, kept positions or distance");
     int rc = -2;
 #define BR_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_runs<DK_, DV_>(q, cache, bias_t, far, sink, cu_seqlens, \
