@@ -161,12 +161,18 @@ def test_cache_write_and_both_attention_kernels(case, dtype):
     bias = dev(relt[distance_buckets(rows, far)], torch.float32)
     sink = torch.zeros(H, dtype=torch.float32, device=DEV)
     tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    import os
     for n_splits in (1, 2, 5, 64):
-        for bias_t in (None, bias.t().contiguous()):          # a block per head; a block per key/value head where built
-            out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
-            KB.attention(q_dev, cache, bias, sink, positions, seq_of_token, table, 64, window, keep, m["scale"], out, H, G,
-                         dk, dv, n_splits=n_splits, bias_t=bias_t)
-            assert rel(out, want) < tol, (n_splits, bias_t is not None)
+        # a block per head; then, where built, a block per key/value head on CUDA cores and on tensor cores
+        for bias_t, form in ((None, ""), (bias.t().contiguous(), "group"), (bias.t().contiguous(), "heads")):
+            os.environ["TQ_BIAS_TOKEN_FORM"] = form
+            try:
+                out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
+                KB.attention(q_dev, cache, bias, sink, positions, seq_of_token, table, 64, window, keep, m["scale"], out, H, G,
+                             dk, dv, n_splits=n_splits, bias_t=bias_t)
+            finally:
+                os.environ.pop("TQ_BIAS_TOKEN_FORM", None)
+            assert rel(out, want) < tol, (n_splits, form)
     if KB.runs_usable(dtype, dk, dv, 64):
         # the same tokens as one run, and as a run that continues a sequence (its first 77 tokens already cached)
         for start in (0, 77):

@@ -712,6 +712,243 @@ bias_attention_runs_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Token form on tensor cores, bfloat16, for several query heads per key/value head: the sixteen rows of
+// mma.sync m16n8k16 are up to sixteen heads of one (token, key/value head).  Grid (token, key/value head x chunks of
+// 16 heads, key range), four warps; the visible positions are walked in tiles of 16 absolute positions (a tile lies
+// in one page: one contiguous piece of the cache), the kept first tiles and then the window's; warp w takes every
+// fourth tile of the block's range through a two-stage cp.async ring of its own.  Scores, mask, bias and online
+// softmax on the accumulator fragments as in the kernel for runs; the warps' states are joined through shared
+// memory in warp order, the ranges' by bias_attention_merge.  The page size is a multiple of 16.
+// ---------------------------------------------------------------------------------------
+#define BH_K 16
+template <int DK, int DV>
+__global__ void __launch_bounds__(BA_WARPS * 32, 3)
+bias_attention_heads_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                            const float* __restrict__ bias_t, int far, const float* __restrict__ sink,
+                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                            const int* __restrict__ page_table, int table_stride, int page_size, int window,
+                            int keep_first, float scale, __nv_bfloat16* __restrict__ out, float* __restrict__ partial,
+                            int n_splits, int nh, int nkv, int n_seqs, int n_pages) {
+    tq_grid_wait();                    // everything below may read what the previous kernel wrote
+    tq_grid_launch_dependents();       // the next kernel's CTAs may move in as SMs free up
+    constexpr int DR = DK + DV, LD = DR + 8;
+    constexpr int STAGE = BH_K * LD;                         // elements of a warp's stage
+    extern __shared__ __align__(16) uint8_t bh_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(bh_smem) + (size_t)warp * 2 * STAGE;
+    const int G_all = nh / nkv;
+    const int chunks = (G_all + 15) / 16;
+    const int t = blockIdx.x, g = blockIdx.y / chunks, chunk = blockIdx.y - g * chunks, split = blockIdx.z;
+    const int h0 = g * G_all + chunk * 16;
+    const int G = min(16, G_all - chunk * 16);
+    const int pos = positions[t];
+    const int* table = page_table + (size_t)TQ_CHECKED(seq_of_token[t], n_seqs, TQ_IDX_SEQUENCE) * table_stride;
+    const int start = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int first = start / BH_K, last = pos / BH_K;
+    const int kept = window > 0 ? min((keep_first + BH_K - 1) / BH_K, first) : 0;
+    const int n_tiles = kept + (last - first + 1);
+    const int per = (n_tiles + n_splits - 1) / n_splits;
+    const int i0 = split * per, i1 = min(n_tiles, i0 + per);
+
+    auto load_tile = [&](int i, int stage) {
+        const int p0 = (i < kept ? i : first + (i - kept)) * BH_K;
+        const int page = TQ_CHECKED(table[TQ_CHECKED(p0 / page_size, table_stride, TQ_IDX_TABLE_COLUMN)], n_pages, TQ_IDX_PAGE);
+        const __nv_bfloat16* src = cache + (((size_t)max(page, 0) * nkv + g) * page_size + p0 % page_size) * DR;
+        __nv_bfloat16* dst = ring + (size_t)stage * STAGE;
+        constexpr int CPR = DR / 8;
+        for (int c = lane; c < BH_K * CPR; c += 32) {
+            const int r = c / CPR, k = c % CPR;
+            br_copy16(dst + r * LD + k * 8, src + r * DR + k * 8);
+        }
+    };
+    if (i0 + warp < i1) load_tile(i0 + warp, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;             // the thread's two rows: heads h0 + r
+    uint32_t qf[DK / 16][4];
+    {
+        const __nv_bfloat16* q_lo = q + ((size_t)t * nh + h0 + r_lo) * DK + (lane & 3) * 2;
+        const __nv_bfloat16* q_hi = q + ((size_t)t * nh + h0 + r_hi) * DK + (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            qf[ks][0] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + ks * 16) : 0u;
+            qf[ks][1] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + ks * 16) : 0u;
+            qf[ks][2] = r_lo < G ? *reinterpret_cast<const uint32_t*>(q_lo + ks * 16 + 8) : 0u;
+            qf[ks][3] = r_hi < G ? *reinterpret_cast<const uint32_t*>(q_hi + ks * 16 + 8) : 0u;
+        }
+    }
+    const float* b_lo = bias_t && r_lo < G ? bias_t + (size_t)(h0 + r_lo) * (far + 1) : nullptr;
+    const float* b_hi = bias_t && r_hi < G ? bias_t + (size_t)(h0 + r_hi) * (far + 1) : nullptr;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+
+    int stage = 0;
+    for (int i = i0 + warp; i < i1; i += BA_WARPS) {
+        if (i + BA_WARPS < i1) load_tile(i + BA_WARPS, stage ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncwarp();                                       // every lane's pieces of this tile have landed
+        const __nv_bfloat16* tile = ring + (size_t)stage * STAGE;
+        const int p_base = (i < kept ? i : first + (i - kept)) * BH_K;
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        const int mi = lane >> 3;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+            uint32_t b[4];
+            br_ldsm4(b, tile + ((mi >> 1) * 8 + (lane & 7)) * LD + ks * 16 + (mi & 1) * 8);
+            br_mma(s[0], qf[ks], b[0], b[1]);
+            br_mma(s[1], qf[ks], b[2], b[3]);
+        }
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int p = p_base + n * 8 + (lane & 3) * 2 + (c & 1);
+                const int d = pos - p;
+                const bool see = d >= 0 && (window == 0 || d < window || p < keep_first);
+                const float* bh = (c & 2) ? b_hi : b_lo;
+                float v = s[n][c] * scale;
+                if (bh && see) v += __ldg(bh + min(d, far));
+                v = see ? v : -INFINITY;
+                s[n][c] = v;
+                if (c & 2) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float u_lo = mn_lo == -INFINITY ? 0.f : mn_lo, u_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float c_lo = __expf(m_lo - u_lo), c_hi = __expf(m_hi - u_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        l_lo *= c_lo; l_hi *= c_hi;
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) { o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi; }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            s[n][0] = __expf(s[n][0] - u_lo); s[n][1] = __expf(s[n][1] - u_lo);
+            s[n][2] = __expf(s[n][2] - u_hi); s[n][3] = __expf(s[n][3] - u_hi);
+            l_lo += s[n][0] + s[n][1];
+            l_hi += s[n][2] + s[n][3];
+        }
+        uint32_t a[4];
+        a[0] = br_pack(s[0][0], s[0][1]);
+        a[1] = br_pack(s[0][2], s[0][3]);
+        a[2] = br_pack(s[1][0], s[1][1]);
+        a[3] = br_pack(s[1][2], s[1][3]);
+#pragma unroll
+        for (int n = 0; n < DV / 8; n += 2) {
+            uint32_t b[4];
+            br_ldsm4_t(b, tile + ((mi & 1) * 8 + (lane & 7)) * LD + DK + (n + (mi >> 1)) * 8);
+            br_mma(o[n], a, b[0], b[1]);
+            br_mma(o[n + 1], a, b[2], b[3]);
+        }
+        __syncwarp();                                       // the stage is filled again two tiles on
+        stage ^= 1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    // the warps' states meet in shared memory (the rings are done with): [warp][row] max and sum, [warp][row][DV]
+    __syncthreads();
+    float* s_m = reinterpret_cast<float*>(bh_smem);
+    float* s_l = s_m + BA_WARPS * 16;
+    float* s_o = s_l + BA_WARPS * 16;
+    if ((lane & 3) == 0) {
+        s_m[warp * 16 + r_lo] = m_lo; s_l[warp * 16 + r_lo] = l_lo;
+        s_m[warp * 16 + r_hi] = m_hi; s_l[warp * 16 + r_hi] = l_hi;
+    }
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+        float* lo = s_o + ((size_t)warp * 16 + r_lo) * DV + n * 8 + (lane & 3) * 2;
+        float* hi = s_o + ((size_t)warp * 16 + r_hi) * DV + n * 8 + (lane & 3) * 2;
+        lo[0] = o[n][0]; lo[1] = o[n][1]; hi[0] = o[n][2]; hi[1] = o[n][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * DV; idx += blockDim.x) {
+        const int r = idx / DV, d = idx % DV;
+        const bool with_sink = sink != nullptr && split == 0;
+        float M = with_sink ? sink[h0 + r] : -INFINITY;
+#pragma unroll
+        for (int w = 0; w < BA_WARPS; ++w) M = fmaxf(M, s_m[w * 16 + r]);
+        float L = with_sink ? expf(sink[h0 + r] - M) : 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < BA_WARPS; ++w) {
+            const float f = s_m[w * 16 + r] == -INFINITY ? 0.f : expf(s_m[w * 16 + r] - M);
+            L += s_l[w * 16 + r] * f;
+            a += s_o[((size_t)w * 16 + r) * DV + d] * f;
+        }
+        if (n_splits == 1) {
+            out[((size_t)t * nh + h0 + r) * DV + d] = __float2bfloat16_rn(a / L);
+            continue;
+        }
+        float* dst = partial + (((size_t)t * nh + h0 + r) * n_splits + split) * (DV + 2);
+        dst[2 + d] = a;
+        if (d == 0) { dst[0] = M; dst[1] = L; }
+    }
+}
+
+template <int DK, int DV>
+int launch_bias_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink, const int* positions,
+                      const int* seq_of_token, const int* page_table, int table_stride, int page_size, int window,
+                      int keep_first, float scale, void* out, float* partial, int n_splits, int T_, int nh, int nkv,
+                      int n_seqs, int n_pages, cudaStream_t stream) {
+    auto kern = bias_attention_heads_kernel<DK, DV>;
+    const int ring = BA_WARPS * 2 * BH_K * (DK + DV + 8) * (int)sizeof(__nv_bfloat16);
+    const int merge = (BA_WARPS * 16 * 2 + BA_WARPS * 16 * DV) * (int)sizeof(float);
+    const int smem = ring > merge ? ring : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) TQ_FAIL(-1, "bias_attention_heads: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int chunks = (nh / nkv + 15) / 16;
+    dim3 grid(T_, nkv * chunks, n_splits);
+    tq_launch(grid, BA_WARPS * 32, smem, stream)(kern, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bias_t, far, sink,
+        positions, seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, (__nv_bfloat16*)out, partial,
+        n_splits, nh, nkv, n_seqs, n_pages);
+    return 0;
+}
+
+TQ_EXPORT int tq_bias_attention_heads(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
+                                      const int* positions, const int* seq_of_token, const int* page_table,
+                                      int table_stride, int page_size, int window, int keep_first, float scale, void* out,
+                                      float* partial, int n_splits, int T_, int nh, int nkv, int dk, int dv, int n_seqs,
+                                      int n_pages, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    TQ_REQUIRE(nkv >= 1 && nh % nkv == 0, "bias_attention_heads: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    TQ_REQUIRE(page_size % BH_K == 0, "bias_attention_heads: pages of %d positions are no multiple of %d", page_size, BH_K);
+    TQ_REQUIRE(window >= 0 && keep_first >= 0 && far >= 0, "bias_attention_heads: negative window, kept positions or distance");
+    TQ_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (long long)nkv * ((nh / nkv + 15) / 16) <= 65535,
+               "bias_attention_heads: %d ranges or %d key/value heads exceed the grid limit", n_splits, nkv);
+    TQ_REQUIRE(n_splits == 1 || partial != nullptr, "bias_attention_heads: %d ranges need scratch for their states", n_splits);
+    int rc = -2;
+#define BH_CASE(DK_, DV_) if (dk == DK_ && dv == DV_) rc = launch_bias_heads<DK_, DV_>(q, cache, bias_t, far, sink, positions, \
+        seq_of_token, page_table, table_stride, page_size, window, keep_first, scale, out, partial, n_splits, T_, nh, nkv,  \
+        n_seqs, n_pages, stream);
+    BH_CASE(32, 32) BH_CASE(32, 64) BH_CASE(32, 128) BH_CASE(64, 32) BH_CASE(64, 64) BH_CASE(64, 128)
+    BH_CASE(128, 32) BH_CASE(128, 64) BH_CASE(128, 128)
+#undef BH_CASE
+    TQ_REQUIRE(rc != -2, "bias_attention_heads: key size %d and value size %d must each be 32, 64 or 128", dk, dv);
+    if (rc) return rc;
+    TQ_CHECK_LAUNCH("bias_attention_heads");
+    if (n_splits > 1) {
+        tq_launch(T_ * nh, dv >= 128 ? 128 : 64, 0, stream)(bias_attention_merge_kernel<__nv_bfloat16>, partial, n_splits, dv, (__nv_bfloat16*)out);
+        TQ_CHECK_LAUNCH("bias_attention_merge");
+    }
+    return 0;
+}
+
 template <int DK, int DV>
 int launch_bias_runs(const void* q, const void* cache, const float* bias_t, int far, const float* sink,
                      const int* cu_seqlens, const int* seq_start, const int* page_table, int table_stride, int window,

@@ -86,13 +86,44 @@ def group_heads(dtype: torch.dtype, dk: int, dv: int, per_kv: int) -> int:
     return int(load_kernel(_LIB).tq_bias_attention_group_heads(c_int(dk), c_int(dv), c_int(per_kv)))
 
 
-def splits_for(n_tokens: int, blocks_per_token: int, longest: int, device) -> int:
-    """Ranges the visible keys of a token are cut into: a step of few tokens is cut until a block has about 64 keys
-    or the launch fills the GPU once (four blocks of four warps an SM); prompts are not cut.  (Measured on B200 at 64
-    tokens x 2 key/value heads x 1,028 keys of 128 + 128: 13 ranges 64.9 us, SPLITS_B64.)  The ranges are joined in
-    range order, so a launch shape always gives the same bits; logits agree across shapes to rounding."""
-    sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return int(max(1, min(64, longest // 64, (4 * sms) // max(1, n_tokens * blocks_per_token))))
+def heads_form(dtype: torch.dtype, dk: int, dv: int, per_kv: int, page_size: int) -> bool:
+    """Whether steps of single tokens take the tensor-core token form (up to sixteen heads of a key/value head are the
+    rows of a tile): bfloat16, sizes of 32, 64 or 128, pages that are multiples of 16, and at least HEADS_FORM_MIN
+    query heads per key/value head (TQ_BIAS_TOKEN_FORM=group|heads forces one)."""
+    import os
+    if dtype != torch.bfloat16 or dk not in RUN_SIZES or dv not in RUN_SIZES or page_size % 16:
+        return False
+    how = os.environ.get("TQ_BIAS_TOKEN_FORM", "")
+    if how in ("group", "heads"):
+        return how == "heads"
+    return per_kv >= HEADS_FORM_MIN
+
+
+HEADS_FORM_MIN = 2
+
+
+def splits_for(n_tokens: int, blocks_per_token: int, longest: int, device, unit: int = 8) -> int:
+    """Ranges the visible keys of a token are cut into.  A block's four warps walk its range in units of `unit` keys
+    (16 in the tensor-core form); three blocks run on an SM at once.  The count that gives the fewest rounds of
+    blocks times units per warp, a block's fixed cost (its queries, the merge) counted as two units, and never fewer
+    than a unit per warp: a step of few tokens is cut until it fills the GPU, a large batch so that its last round
+    of blocks is full.  (Measured on B200 at 64 tokens x 4 key/value heads x 1,028 keys of 128 + 128, tensor-core
+    form: SPLITS_NOTE.)  The ranges are joined in range order, so a launch shape always gives the same bits; logits
+    agree across shapes to rounding."""
+    import os
+    forced = os.environ.get("TQ_BIAS_SPLITS", "")
+    if forced:
+        return max(1, min(64, int(forced)))
+    slots = 3 * torch.cuda.get_device_properties(device).multi_processor_count
+    units = -(-max(1, longest) // unit)
+    best, best_cost = 1, float("inf")
+    for s in range(1, min(64, max(1, units // 4)) + 1):
+        per_block = -(-(-(-units // s)) // 4) + 2
+        rounds = -(-(n_tokens * blocks_per_token * s) // slots)
+        cost = rounds * per_block + 0.05 * s
+        if cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, bias: Optional[torch.Tensor], sink: Optional[torch.Tensor],
@@ -117,6 +148,13 @@ def attention(q: torch.Tensor, cache: torch.Tensor, bias: Optional[torch.Tensor]
         want_f32(sink, "the sink")
     partial = torch.empty(T * heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
     lib = load_kernel(_LIB)
+    if (bias is None or bias_t is not None) and heads_form(q.dtype, dk, dv, heads // kv_heads, page_size):
+        check(_LIB, lib.tq_bias_attention_heads(
+            ptr(q), ptr(cache), ptr(bias_t), c_int(far), ptr(sink), ptr(positions), ptr(seq_of_token), ptr(page_table),
+            c_int(page_table.shape[1]), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), ptr(out),
+            ptr(partial), c_int(n_splits), c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+            c_int(page_table.shape[0]), c_int(cache.shape[0]), stream()), kernels=2 if n_splits > 1 else 1)
+        return out
     if (bias is None or bias_t is not None) and page_size % 8 == 0 and group_heads(q.dtype, dk, dv, heads // kv_heads):
         check(_LIB, lib.tq_bias_attention_group(
             ptr(q), ptr(cache), ptr(bias_t), c_int(far), ptr(sink), ptr(positions), ptr(seq_of_token), ptr(page_table),

@@ -143,9 +143,12 @@ class BiasedWindowAttentionMixer(Mixer):
             per_kv = self.heads // self.kv_heads
             gc = KB.group_heads(act, self.dim, self.vdim, per_kv)
             blocks = self.kv_heads * -(-per_kv // gc) if gc else self.heads
+            unit = 8
+            if KB.heads_form(act, self.dim, self.vdim, per_kv, cache.page_size):
+                blocks, unit = self.kv_heads * -(-per_kv // 16), 16
             KB.attention(q, cache.kv, self.bias, self.sink, ctx.positions, ctx.seq_of_token, cache.page_table,
                          cache.page_size, self.window, self.keep_first, self.scale, o, self.heads, self.kv_heads,
-                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev), bias_t=self.bias_t)
+                         self.dim, self.vdim, n_splits=KB.splits_for(T, blocks, longest, dev, unit), bias_t=self.bias_t)
         if KG.pays(o, self.w_o):                   # a few tokens: the output projection as a stream of its weights
             return KG.gemv(o, self.w_o, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
         return linear(o, self.w_o, out_dtype=torch.float32)
